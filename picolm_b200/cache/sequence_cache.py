@@ -116,7 +116,8 @@ class SequenceCache:
             for g in self.kv_groups:
                 shape = (len(g.layers), n_pages + 1, g.spec.num_kv_heads, PAGE_TOKENS, g.spec.head_dim)
                 g.k = torch.zeros(shape, dtype=kv_dtype, device=self.device)
-                g.v = torch.zeros(shape, dtype=kv_dtype, device=self.device)
+                # a group without values of its own (a latent cache): what is kept serves as key and as value
+                g.v = torch.zeros(shape, dtype=kv_dtype, device=self.device) if g.spec.values else g.k
             for layer, spec in self.state_specs.items():
                 self.state[layer] = torch.zeros((max_seqs + 1,) + spec.shape, dtype=_STATE_DTYPES[spec.dtype],
                                                 device=self.device)
@@ -224,4 +225,5 @@ class SequenceCache:
 
     def kv_bytes_per_token(self) -> int:
         item = torch.empty((), dtype=self.kv_dtype).element_size()
-        return sum(2 * len(g.layers) * g.spec.num_kv_heads * g.spec.head_dim * item for g in self.kv_groups)
+        return sum((2 if g.spec.values else 1) * len(g.layers) * g.spec.num_kv_heads * g.spec.head_dim * item
+                   for g in self.kv_groups)

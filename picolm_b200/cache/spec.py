@@ -18,20 +18,21 @@ class CacheSpec:
     num_kv_heads: int = 0                       # kv
     head_dim: int = 0                           # kv
     window: Optional[int] = None                # kv: keep only the last `window` positions
+    values: bool = True                         # kv: False = one row per position that serves as key and as value
     shape: Tuple[int, ...] = ()                 # state: per-sequence shape
     dtype: str = "float32"                      # state: element type
 
     @staticmethod
-    def kv(num_kv_heads: int, head_dim: int, window: Optional[int] = None) -> "CacheSpec":
+    def kv(num_kv_heads: int, head_dim: int, window: Optional[int] = None, values: bool = True) -> "CacheSpec":
         if num_kv_heads <= 0 or head_dim <= 0:
             raise ValueError("a kv cache needs positive num_kv_heads and head_dim")
         if window is not None and window <= 0:
             raise ValueError("a window must be positive")
-        return CacheSpec("kv", num_kv_heads=num_kv_heads, head_dim=head_dim, window=window)
+        return CacheSpec("kv", num_kv_heads=num_kv_heads, head_dim=head_dim, window=window, values=bool(values))
 
     @staticmethod
     def state(shape, dtype: str = "float32") -> "CacheSpec":
         return CacheSpec("state", shape=tuple(int(s) for s in shape), dtype=dtype)
 
     def group_key(self):
-        return (self.kind, self.num_kv_heads, self.head_dim, self.window, self.shape, self.dtype)
+        return (self.kind, self.num_kv_heads, self.head_dim, self.window, self.shape, self.dtype, self.values)

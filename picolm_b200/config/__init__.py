@@ -1,9 +1,10 @@
 from .llama import ConfigError, LlamaConfig, RopeScaling
+from .potuzen import PotuzenConfig, PotuzenLayer
 from .registry import (architecture_of, config_from_dict, read_config, register_architecture,
                        registered_architectures, spec_of)
 from .spec import LayerSpec, ModelSpec, PartSpec
 
 __all__ = [
-    "ConfigError", "LlamaConfig", "RopeScaling", "architecture_of", "config_from_dict", "read_config",
+    "ConfigError", "LlamaConfig", "PotuzenConfig", "PotuzenLayer", "RopeScaling", "architecture_of", "config_from_dict", "read_config",
     "register_architecture", "registered_architectures", "spec_of", "LayerSpec", "ModelSpec", "PartSpec",
 ]

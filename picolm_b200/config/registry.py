@@ -37,9 +37,12 @@ def registered_architectures():
 
 def architecture_of(raw: Mapping[str, Any]) -> Architecture:
     archs = raw.get("architectures")
+    if isinstance(raw.get("architecture"), str) and not archs:
+        archs = [raw["architecture"]]                # some designs name themselves with one string
     if not archs or not isinstance(archs, (list, tuple)):
         raise KeyError(
-            "config.json lacks the key 'architectures'; registered: " + ", ".join(registered_architectures()))
+            "config.json lacks the key 'architectures' (or 'architecture'); registered: "
+            + ", ".join(registered_architectures()))
     name = str(archs[0])
     if name not in _ARCHITECTURES:
         raise KeyError(

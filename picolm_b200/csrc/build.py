@@ -41,6 +41,7 @@ LIBRARIES: Dict[str, List[str]] = {
     "attention_mma": ["attention_mma.cu"],          # one variant per head size: "attention_mma@hd64" with -DPLM_HD=64
     "attention_tc": ["attention_tc.cu"],            # likewise, head sizes 64 and 128
     "sampling": ["sampling.cu"],
+    "recurrent": ["recurrent.cu"],
 }
 HEADERS = ["common.cuh", "tc_common.cuh", "gemm_tc_static.h"]
 

@@ -13,4 +13,6 @@ from .elementwise import GATE_ACTIVATIONS, embed, gather_rows, rmsnorm, rope_sto
 from .gemm import (PendingLinear, ScaledRows, gemm_simt, gemm_tc_skinny, gemm_tc_supported,  # noqa: F401
                    gemm_tc_wide, interleave_gate_up, linear, linear_residual_norm, linear_swiglu, pair_pays,
                    residual_norm_supported)
+from .recurrent import (DECAY_SIGMOID, DECAY_STEP, GATE_AFTER_NORM, GATE_BEFORE_NORM, GATE_NONE, causal_conv,  # noqa: F401
+                        gated_norm, head_linear, linear_scan, store_rows_paged)
 from .sampling import argmax, sample  # noqa: F401

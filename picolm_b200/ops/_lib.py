@@ -46,6 +46,12 @@ _SIGNATURES = {
     "plm_decode_chain": [_vp, _i, _i, _vp, _vp, _vp, _vp],
     "plm_decode_chain_ctas": [],
     "plm_decode_chain_scratch": [_i, _i, _i],
+    "plm_causal_conv": [_vp, _i, _l, _vp, _vp, _vp, _l, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
+    "plm_linear_scan": [_vp, _vp, _vp, _vp, _i, _l, _l, _l, _l, _i, _vp, _vp, _vp, _f, _f, _vp, _l, _vp, _l, _vp, _vp,
+                        _i, _i, _i, _i, _i, _vp],
+    "plm_gated_norm": [_vp, _i, _l, _vp, _i, _l, _vp, _i, _vp, _i, _l, _i, _i, _i, _f, _i, _i, _i, _vp],
+    "plm_head_linear": [_vp, _i, _l, _vp, _vp, _l, _vp, _l, _i, _i, _i, _i, _vp],
+    "plm_store_rows_paged": [_vp, _i, _l, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
     "plm_argmax": [_vp, _l, _i, _i, _vp, _vp],
     "plm_sample": [_vp, _l, _i, _i, _f, _i, _f, _f, _vp, _vp, _vp],
 }
@@ -56,7 +62,7 @@ _fn_cache = {}
 # this package hand them the bounds before every launch.  An index outside its bound is then recorded in
 # the status word (`check_status` raises) instead of being followed.
 CHECKED = os.environ.get("PICOLM_B200_CHECK", "") == "1"
-CHECKED_LIBRARIES = ("elementwise", "attention_simt", "attention_mma", "attention_tc")
+CHECKED_LIBRARIES = ("elementwise", "attention_simt", "attention_mma", "attention_tc", "recurrent")
 
 
 class KernelError(RuntimeError):

@@ -1,0 +1,172 @@
+"""Faces of the kernels for mixers with a fixed-size state (csrc/recurrent.cu): the depthwise causal
+convolution, the gated linear recurrence, the gate-and-norm step, one small matrix per head, and rows
+written into the pages of a cache."""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ._lib import PAGE_TOKENS, KernelError, _check, _dev, _dt, _fn, _i32, _p, _stream, set_bounds
+
+DECAY_STEP, DECAY_SIGMOID = 1, 2
+
+
+def _cols(t: torch.Tensor, name: str) -> int:
+    """A matrix whose rows are contiguous (it may be a slice of columns of a wider one); returns its row stride."""
+    if not t.is_cuda:
+        raise KernelError(f"{name} is on {t.device}; picolm_b200 kernels run on a CUDA device only")
+    if t.dim() != 2 or (t.shape[1] > 1 and t.stride(1) != 1):
+        raise KernelError(f"{name} must be a matrix with contiguous rows")
+    return t.stride(0)
+
+
+def _f32(t: Optional[torch.Tensor], name: str, numel: int) -> None:
+    if t is None:
+        return
+    _dev(t, name)
+    if t.dtype != torch.float32 or t.numel() != numel:
+        raise KernelError(f"{name} must be float32 with {numel} elements")
+
+
+def causal_conv(u: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor, step) -> torch.Tensor:
+    """Depthwise causal convolution over each sequence's tokens followed by SiLU.  `u` [T, C] (a column slice
+    will do), `weight` [C, taps] float32 with the current token's tap last, `bias` [C] float32 or None, `state`
+    float32 [slots, >= (taps - 1) * C] with contiguous rows: the last taps - 1 inputs of every sequence, oldest
+    first; it is read for the tokens before the step's first and brought up to date.  Returns [T, C] like u."""
+    ldu = _cols(u, "u")
+    T, C = u.shape
+    taps = weight.shape[1]
+    _f32(weight, "weight", C * taps), _f32(bias, "bias", C)
+    lds = _cols(state, "state")
+    if state.dtype != torch.float32 or state.shape[1] < (taps - 1) * C:
+        raise KernelError("causal_conv: the state must be float32 with (taps - 1) * C values a row")
+    out = torch.empty((T, C), dtype=u.dtype, device=u.device)
+    decode = bool(step.is_decode and step.n_tokens == step.n_seqs)
+    set_bounds("recurrent", n_seqs=step.n_seqs, device=u.device)
+    _check(_fn("recurrent", "plm_causal_conv")(
+        _p(u), _dt(u, "u"), ldu, _p(weight), _p(bias), _p(state), lds, _p(step.tok_seq), _p(step.seq_start),
+        _p(step.seq_slot), _p(out), T, step.n_seqs, C, taps, 1 if decode else 0, _stream()),
+        f"causal_conv T={T} C={C} taps={taps}", kernels=1 if decode or taps == 1 else 2,
+        nbytes=2 * T * C * u.element_size())
+    return out
+
+
+def linear_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, raw: torch.Tensor, mode: int, p0: torch.Tensor,
+                p1: Optional[torch.Tensor], skip: Optional[torch.Tensor], q_scale: float, power: float,
+                state: torch.Tensor, step, heads: int, key_dim: int, value_dim: int, heads_per_group: int = 1) -> torch.Tensor:
+    """The recurrence S_t = diag(d_t) S_(t-1) + k_t v_t^T, y_t = S_t^T (q_scale q_t) (+ skip[h] v_t) over each
+    sequence's tokens, per head, everything in float32; returns y [T, heads * value_dim] float32.
+
+    q, k [T, groups * key_dim] (head h reads group h // heads_per_group), v [T, heads * value_dim]; column slices
+    will do.  The decay comes from `raw`:
+      DECAY_STEP     raw [T, heads]: dt = softplus(raw + p0[h]), d = exp(-exp(p1[h]) dt) for the whole head, and
+                     v_t enters the state times dt (the skip term takes it unscaled)
+      DECAY_SIGMOID  raw [T, heads * key_dim]: d[n] = sigmoid(raw + p0[h, n]) ** power
+    `state` float32 [slots, >= heads * key_dim * value_dim] with contiguous rows holds S of every sequence as
+    [heads, key_dim, value_dim] and is carried on."""
+    ldq, ldk, ldv, ldr = _cols(q, "q"), _cols(k, "k"), _cols(v, "v"), _cols(raw, "raw")
+    T = v.shape[0]
+    H, N, P = heads, key_dim, value_dim
+    if H % heads_per_group:
+        raise KernelError("linear_scan: heads is not a multiple of heads_per_group")
+    G = H // heads_per_group
+    if q.shape != (T, G * N) or k.shape != (T, G * N) or v.shape != (T, H * P) or not (q.dtype == k.dtype == v.dtype == raw.dtype):
+        raise KernelError("linear_scan: q, k, v do not have the shapes the head counts imply, or differ in type")
+    if mode == DECAY_STEP:
+        if raw.shape != (T, H):
+            raise KernelError("linear_scan: a decay per head wants raw [T, heads]")
+        _f32(p0, "p0", H), _f32(p1, "p1", H)
+        if p1 is None:
+            raise KernelError("linear_scan: a decay per head wants p1 (the logarithm of the rate)")
+    elif mode == DECAY_SIGMOID:
+        if raw.shape != (T, H * N):
+            raise KernelError("linear_scan: a decay per key channel wants raw [T, heads * key_dim]")
+        _f32(p0, "p0", H * N)
+    else:
+        raise KernelError(f"linear_scan: unknown decay mode {mode}")
+    _f32(skip, "skip", H)
+    if N > 256:
+        raise KernelError(f"linear_scan: key_dim {N} exceeds 256, the largest state a thread's registers take")
+    lds = _cols(state, "state")
+    if state.dtype != torch.float32 or state.shape[1] < H * N * P:
+        raise KernelError("linear_scan: the state must be float32 with heads * key_dim * value_dim values a row")
+    y = torch.empty((T, H * P), dtype=torch.float32, device=v.device)
+    _check(_fn("recurrent", "plm_linear_scan")(
+        _p(q), _p(k), _p(v), _p(raw), _dt(v, "v"), ldq, ldk, ldv, ldr, mode, _p(p0), _p(p1), _p(skip), float(q_scale),
+        float(power), _p(state), lds, _p(y), H * P, _p(step.seq_start), _p(step.seq_slot), step.n_seqs, H, N, P,
+        heads_per_group, _stream()), f"linear_scan T={T} H={H} N={N} P={P}",
+        nbytes=T * (2 * G * N + H * P) * v.element_size() + T * H * P * 4 + 2 * step.n_seqs * H * N * P * 4,
+        flops=6 * T * H * N * P)
+    return y
+
+
+GATE_NONE, GATE_BEFORE_NORM, GATE_AFTER_NORM = 0, 1, 2
+_ACTS = {"silu": 0, "sigmoid": 1}
+
+
+def gated_norm(x: torch.Tensor, out_dtype: torch.dtype, weight: Optional[torch.Tensor] = None, eps: float = 0.0,
+               group: Optional[int] = None, weight_per_group: bool = False, gate: Optional[torch.Tensor] = None,
+               gate_mode: int = GATE_NONE, activation: str = "silu", norm: bool = True) -> torch.Tensor:
+    """Rows of `x` [T, C] (float32 or the run's type; a column slice will do), in groups of `group` columns
+    (default: the whole row): optionally times act(gate) first, then each group divided by its root mean square
+    (eps inside the root) and multiplied by `weight` (float32, [C], or [group] with `weight_per_group`), optionally
+    times act(gate) afterwards.  With `norm=False` only the gate is applied.  Returns [T, C] of `out_dtype`."""
+    ldx = _cols(x, "x")
+    T, C = x.shape
+    group = C if group is None else int(group)
+    if group <= 0 or C % group:
+        raise KernelError(f"gated_norm: {C} columns do not come in groups of {group}")
+    if weight is not None:
+        _f32(weight, "weight", group if weight_per_group else C)
+    if activation not in _ACTS:
+        raise KernelError(f"gated_norm: activation {activation!r} is not known ({', '.join(_ACTS)})")
+    ldg = 0
+    if gate_mode != GATE_NONE:
+        if gate is None or gate.shape != x.shape:
+            raise KernelError("gated_norm: the gate must be shaped like x")
+        ldg = _cols(gate, "gate")
+    else:
+        gate = None
+    out = torch.empty((T, C), dtype=out_dtype, device=x.device)
+    _check(_fn("recurrent", "plm_gated_norm")(
+        _p(x), _dt(x, "x"), ldx, _p(gate), _dt(gate, "gate") if gate is not None else 1, ldg, _p(weight),
+        1 if weight_per_group else 0, _p(out), _dt(out, "out"), C, T, C, group, float(eps), int(gate_mode),
+        _ACTS[activation], 1 if norm else 0, _stream()), f"gated_norm T={T} C={C} group={group}",
+        nbytes=T * C * (x.element_size() + out.element_size() + (gate.element_size() if gate is not None else 0)))
+    return out
+
+
+def head_linear(x: torch.Tensor, weight: torch.Tensor, gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[t, h, :] = weight[h] @ x[t, h, :] for `weight` [H, O, I] and `x` [T, H * I] (a column slice will do), with
+    float32 sums; optionally times sigmoid(gate) for `gate` [T, H * O].  Returns [T, H * O] of x's type."""
+    ldx = _cols(x, "x")
+    _dev(weight, "weight")
+    H, O, I = weight.shape
+    T = x.shape[0]
+    if x.shape[1] != H * I or weight.dtype != x.dtype:
+        raise KernelError(f"head_linear: x is {tuple(x.shape)} of {x.dtype}, the weights are {tuple(weight.shape)} of {weight.dtype}")
+    ldg = 0
+    if gate is not None:
+        ldg = _cols(gate, "gate")
+        if gate.shape != (T, H * O) or gate.dtype != x.dtype:
+            raise KernelError("head_linear: the gate must be [T, H * O] of x's type")
+    out = torch.empty((T, H * O), dtype=x.dtype, device=x.device)
+    _check(_fn("recurrent", "plm_head_linear")(
+        _p(x), _dt(x, "x"), ldx, _p(weight), _p(gate), ldg, _p(out), H * O, T, H, O, I, _stream()),
+        f"head_linear T={T} H={H} {O}x{I}", nbytes=(T * H * (I + O) + H * O * I) * x.element_size(), flops=2 * T * H * O * I)
+    return out
+
+
+def store_rows_paged(rows: torch.Tensor, pages: torch.Tensor, step, block_table: torch.Tensor) -> None:
+    """Row t of `rows` [T, R] into `pages` [n_pages, 1, PAGE_TOKENS, R] at position tok_pos[t] of sequence tok_seq[t]."""
+    ld = _cols(rows, "rows")
+    _dev(pages, "pages"), _i32(block_table, "block_table")
+    T, R = rows.shape
+    if pages.dtype != rows.dtype or tuple(pages.shape[1:]) != (1, PAGE_TOKENS, R):
+        raise KernelError(f"store_rows_paged: the pages must be [n, 1, {PAGE_TOKENS}, {R}] of {rows.dtype}")
+    set_bounds("recurrent", n_pages=pages.shape[0], n_seqs=block_table.shape[0],
+               n_positions=block_table.shape[1] * PAGE_TOKENS, device=rows.device)
+    _check(_fn("recurrent", "plm_store_rows_paged")(
+        _p(rows), _dt(rows, "rows"), ld, _p(pages), _p(step.tok_pos), _p(step.tok_seq), _p(block_table),
+        block_table.shape[1], T, R, _stream()), f"store_rows_paged T={T} R={R}", nbytes=2 * T * R * rows.element_size())

@@ -36,12 +36,16 @@ FAMILIES = ("norm", "mixer", "feed_forward", "position", "arrangement", "embeddi
 @dataclass(frozen=True)
 class WeightSpec:
     """A tensor a part wants.  `init` tells the random-weights mode how to fill
-    it: "normal" N(0, std), "ones_normal" 1 + N(0, norm_std), "zeros"; `integer`
-    tensors are kept as int32."""
+    it: "normal" N(0, std), "ones_normal" 1 + N(0, norm_std), "zeros", "uniform" U(lo, hi),
+    "normal_scaled" N(0, scale); `integer` tensors are kept as int32.  A size of -1 in `shape` is whatever
+    the checkpoint has there (the part reads it off the tensor in `load`)."""
 
     shape: Tuple[int, ...]
     init: str = "normal"
     integer: bool = False
+    lo: float = 0.0
+    hi: float = 1.0
+    scale: float = 1.0
 
 
 class Part:

@@ -95,3 +95,45 @@ def pre_norm_layer(prefix: str, mixer: PartSpec, feed_forward: PartSpec, mixer_n
         "mixer_norm": ("norm", mixer_norm), "mixer": ("mixer", mixer),
         "feed_forward_norm": ("norm", feed_forward_norm), "feed_forward": ("feed_forward", feed_forward),
     }, cache_of=cache_of)
+
+
+@register_part("arrangement", "sandwich_norm")
+class SandwichNormBlock(Arrangement):
+    """A norm before and a norm after each sublayer: `x += post(mixer(pre(x))); x += post'(feed_forward(pre'(x)))`.
+    The norms after the sublayers work on the sublayer's float32 result, before it is added to the stream.  The
+    feed-forward and its two norms are optional (a layer that only mixes)."""
+
+    wants = ("mixer_norm", "mixer", "mixer_post_norm")
+    narrows_rows = True
+
+    @staticmethod
+    def _rows(delta):
+        return delta.compute() if hasattr(delta, "compute") else delta
+
+    def forward(self, stream, step, caches, keep_rows=None):
+        h = self.mixer_norm.forward(stream)
+        delta = self._rows(self.mixer.forward(h, step, caches[0] if caches else None))
+        if keep_rows is not None:
+            # the last layer of a step: only these rows are read afterwards, and the norms go row by row
+            if keep_rows.numel() == 0:
+                stream.pending = None
+                return
+            stream.pending = delta
+            stream.narrow(keep_rows)
+            delta = stream.pending
+        stream.pending = self.mixer_post_norm.normalize(delta)
+        if "feed_forward" not in self.named:
+            return
+        h = self.feed_forward_norm.forward(stream)
+        stream.pending = self.feed_forward_post_norm.normalize(self._rows(self.feed_forward.forward(h, step)))
+
+
+def sandwich_norm_layer(prefix: str, mixer: PartSpec, mixer_norm: PartSpec, mixer_post_norm: PartSpec,
+                        feed_forward: PartSpec = None, feed_forward_norm: PartSpec = None,
+                        feed_forward_post_norm: PartSpec = None, cache_of=None) -> LayerSpec:
+    """The spec of a `sandwich_norm` layer; without `feed_forward` the layer only mixes."""
+    parts = {"mixer_norm": ("norm", mixer_norm), "mixer": ("mixer", mixer), "mixer_post_norm": ("norm", mixer_post_norm)}
+    if feed_forward is not None:
+        parts.update({"feed_forward_norm": ("norm", feed_forward_norm), "feed_forward": ("feed_forward", feed_forward),
+                      "feed_forward_post_norm": ("norm", feed_forward_post_norm)})
+    return LayerSpec(prefix, "sandwich_norm", parts, cache_of=cache_of)

@@ -15,13 +15,18 @@ from .stream import ResidualStream
 
 @register_part("norm", "rmsnorm")
 class RMSNorm(Part):
-    """params: size, eps.  Weight: `weight` [size]."""
+    """params: size, eps, name (the weight's tensor name relative to the part's prefix; default "weight", ""
+    for a tensor that is called by the prefix alone).  Weight: [size]."""
+
+    @property
+    def _name(self) -> str:
+        return self.params.get("name", "weight")
 
     def weight_specs(self):
-        return {"weight": WeightSpec((self.params["size"],), init="ones_normal")}
+        return {self._name: WeightSpec((self.params["size"],), init="ones_normal")}
 
     def load(self, tensors):
-        self.weight = tensors["weight"]
+        self.weight = tensors[self._name]
 
     def weight_bytes(self):
         return self.weight.numel() * self.weight.element_size()
@@ -48,3 +53,8 @@ class RMSNorm(Part):
         if rows is None:
             stream.pending = None
         return h
+
+    def normalize(self, rows: torch.Tensor) -> torch.Tensor:
+        """The norm of float32 rows that are not the stream (a sublayer's result, normalised before it is added);
+        float32 [T, size]."""
+        return ops.rmsnorm(rows, self.weight, self.params["eps"], torch.float32)

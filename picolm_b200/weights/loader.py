@@ -58,7 +58,7 @@ def check_checkpoint(expected: Dict[str, WeightSpec], ckpt: Checkpoint, ignored=
         if ent is None:
             missing.append((name, ws.shape))
             continue
-        if tuple(ent.shape) != tuple(ws.shape):
+        if len(ent.shape) != len(ws.shape) or any(w not in (-1, e) for w, e in zip(ws.shape, ent.shape)):   # -1: any size
             wrong_shape.append((name, ws.shape, ent.shape))
         if ws.integer and ent.dtype not in _INTS:
             wrong_dtype.append((name, ent.dtype, "an integer table is expected"))

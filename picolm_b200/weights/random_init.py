@@ -31,12 +31,19 @@ def random_tensors(config, seed: int, std: float = 0.02, norm_std: float = 0.1,
     expected = model.expected_tensors()
     for name in sorted(expected):
         ws = expected[name]
+        if any(n < 0 for n in ws.shape):
+            raise ValueError(f"tensor {name!r}: its shape {ws.shape} leaves a size to the checkpoint; random weights "
+                             f"need that size in the configuration")
         if ws.integer or ws.init == "zeros":
             out[name] = torch.zeros(ws.shape, dtype=torch.int32 if ws.integer else dt)
         elif ws.init == "ones_normal":
             out[name] = (1.0 + norm_std * torch.randn(ws.shape, generator=gen, dtype=torch.float32)).to(dt)
         elif ws.init == "normal":
             out[name] = (std * torch.randn(ws.shape, generator=gen, dtype=torch.float32)).to(dt)
+        elif ws.init == "uniform":
+            out[name] = (ws.lo + (ws.hi - ws.lo) * torch.rand(ws.shape, generator=gen, dtype=torch.float32)).to(dt)
+        elif ws.init == "normal_scaled":
+            out[name] = (ws.scale * torch.randn(ws.shape, generator=gen, dtype=torch.float32)).to(dt)
         else:
             raise ValueError(f"tensor {name!r}: unknown init {ws.init!r}")
     return out
