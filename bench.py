@@ -220,7 +220,20 @@ def main():
                     help="with the other points: one request's decode rate after a prompt of this many tokens (0: skip)")
     ap.add_argument("--no-graphs", action="store_true",
                     help="launch every kernel of a decode step by itself (for a profiler's launch list)")
+    ap.add_argument("--design", default="", choices=["", "potuzen"],
+                    help="instead of the headline: prefill and decode throughput of this design beside the Llama decoder "
+                         "at equal layer sizes (random weights); prints one JSON line of its own")
+    ap.add_argument("--design-sizes", default="w2048,w4096", help="with --design: which sizes (w2048, w4096)")
+    ap.add_argument("--design-prompt", type=int, default=2048, help="with --design: tokens of the timed prompt")
+    ap.add_argument("--design-kernels", action="store_true",
+                    help="with --design: time every kind of launch by itself and give its roofline fractions")
     args = ap.parse_args()
+    if args.design:
+        if args.gpus != 1:
+            print(f"picolm_b200 is a one-GPU library: --gpus {args.gpus} is not supported, run with --gpus 1")
+            return 2
+        from picolm_b200 import bench_designs
+        return bench_designs.main(args)
     if args.gpus != 1:
         print(f"picolm_b200 is a one-GPU library: --gpus {args.gpus} is not supported, run with --gpus 1")
         return 2
