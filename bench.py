@@ -232,6 +232,8 @@ def main():
         if args.gpus != 1:
             print(f"picolm_b200 is a one-GPU library: --gpus {args.gpus} is not supported, run with --gpus 1")
             return 2
+        if args.design_kernels:
+            os.environ["PICOLM_B200_TRACE"] = "1"      # read when the package is imported: every launch between two events
         from picolm_b200 import bench_designs
         return bench_designs.main(args)
     if args.gpus != 1:

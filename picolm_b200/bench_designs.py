@@ -134,8 +134,10 @@ def run(design: str, sizes, prompt_tokens: int, batch: int, steps: int, warmup: 
 
 
 def main(args) -> int:
-    if args.design_kernels:
-        os.environ["PICOLM_B200_TRACE"] = "1"          # read when the package is imported: every launch between two events
+    from picolm_b200.ops import _lib
+    if args.design_kernels and not _lib.TRACED:
+        print("the per-launch table needs PICOLM_B200_TRACE=1 in the environment before the package is imported")
+        return 2
     sizes = [s for s in args.design_sizes.split(",") if s]
     for s in sizes:
         if s not in SIZES:

@@ -54,7 +54,10 @@ VARIANTS: Dict[str, Dict[str, List[str]]] = {
 
 
 # Variants of libraries that also exist plain: (name, flags).  The build check builds them too.
-MORE_BUILDS: List = [("gemm_tc_wide@stream", ["-DPLM_WIDE_STREAM"])]
+MORE_BUILDS: List = [("gemm_tc_wide@stream", ["-DPLM_WIDE_STREAM"]),
+                     # the gated epilogue with the tanh form of GELU in place of SiLU
+                     ("gemm_tc_skinny@gelu", ["-DPLM_GATE_GELU"]), ("gemm_tc_wide@gelu", ["-DPLM_GATE_GELU"]),
+                     ("gemm_tc_wide@stream_gelu", ["-DPLM_WIDE_STREAM", "-DPLM_GATE_GELU"])]
 
 
 def attention_variant(head_dim: int, family: str = "attention_mma"):

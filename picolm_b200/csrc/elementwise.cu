@@ -165,6 +165,84 @@ extern "C" int plm_rmsnorm(float* x, const float* delta, const void* w, int w_dt
     return PLM_ERR_DTYPE;
 }
 
+// A sublayer's result normalised, added to the stream, and the new stream normalised for the next sublayer, in
+// one pass over the row: x += (delta * r1) * w_post with r1 from delta's mean square; out = (x * r2) * w_pre with
+// r2 from the new x's.  The same roundings as the two kernels it replaces (each product rounded, then the sum).
+// Rows whose width is a multiple of 4 and at most 16 * NT stay in registers throughout.
+template <typename Tw, typename To, int NT>
+__global__ void __launch_bounds__(NT)
+post_pre_norm_kernel(float* __restrict__ x, const float* __restrict__ delta, const Tw* __restrict__ w_post,
+                     const Tw* __restrict__ w_pre, To* __restrict__ out, int d, float eps_post, float eps_pre) {
+    __shared__ float red[33];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int r = blockIdx.x;
+    float* xr = x + (size_t)r * d;
+    const float* dr = delta + (size_t)r * d;
+    float4 v[4];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int i = (threadIdx.x + k * NT) * 4;
+        if (i < d) {
+            v[k] = load4(dr + i);
+            ss += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+        }
+    }
+    ss = block_sum<NT>(ss, red);
+    const float s1 = 1.0f / sqrtf(ss / (float)d + eps_post);
+    ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int i = (threadIdx.x + k * NT) * 4;
+        if (i < d) {
+            const float4 wv = load4(w_post + i), xv = load4(xr + i);
+            v[k].x = __fadd_rn(xv.x, __fmul_rn(__fmul_rn(v[k].x, s1), wv.x));
+            v[k].y = __fadd_rn(xv.y, __fmul_rn(__fmul_rn(v[k].y, s1), wv.y));
+            v[k].z = __fadd_rn(xv.z, __fmul_rn(__fmul_rn(v[k].z, s1), wv.z));
+            v[k].w = __fadd_rn(xv.w, __fmul_rn(__fmul_rn(v[k].w, s1), wv.w));
+            store4(xr + i, v[k]);
+            ss += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+        }
+    }
+    ss = block_sum<NT>(ss, red);
+    const float s2 = 1.0f / sqrtf(ss / (float)d + eps_pre);
+    To* o = out + (size_t)r * d;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int i = (threadIdx.x + k * NT) * 4;
+        if (i < d) {
+            const float4 wv = load4(w_pre + i);
+            store4(o + i, make_float4(v[k].x * s2 * wv.x, v[k].y * s2 * wv.y, v[k].z * s2 * wv.z, v[k].w * s2 * wv.w));
+        }
+    }
+}
+
+template <typename Tw, typename To>
+static int post_pre_norm_launch(float* x, const float* delta, const void* w_post, const void* w_pre, void* out, int n_rows,
+                                int d, float eps_post, float eps_pre, cudaStream_t stream) {
+    if (d <= 16 * 256)
+        return plm_status_of(launch_pdl(post_pre_norm_kernel<Tw, To, 256>, n_rows, 256, 0, stream, x, delta, (const Tw*)w_post,
+                                        (const Tw*)w_pre, (To*)out, d, eps_post, eps_pre));
+    return plm_status_of(launch_pdl(post_pre_norm_kernel<Tw, To, 1024>, n_rows, 1024, 0, stream, x, delta, (const Tw*)w_post,
+                                    (const Tw*)w_pre, (To*)out, d, eps_post, eps_pre));
+}
+
+extern "C" int plm_post_pre_norm(float* x, const float* delta, const void* w_post, const void* w_pre, int w_dtype, void* out,
+                                 int out_dtype, int n_rows, int d, float eps_post, float eps_pre, cudaStream_t stream) {
+    if (n_rows <= 0) return PLM_OK;
+    if (d <= 0 || d % 4 || d > 16 * 1024) return PLM_ERR_SHAPE;
+    if (w_dtype == PLM_F32 && out_dtype == PLM_F32)
+        return post_pre_norm_launch<float, float>(x, delta, w_post, w_pre, out, n_rows, d, eps_post, eps_pre, stream);
+    if (w_dtype == PLM_BF16 && out_dtype == PLM_F32)
+        return post_pre_norm_launch<bf16, float>(x, delta, w_post, w_pre, out, n_rows, d, eps_post, eps_pre, stream);
+    if (w_dtype == PLM_F32 && out_dtype == PLM_BF16)
+        return post_pre_norm_launch<float, bf16>(x, delta, w_post, w_pre, out, n_rows, d, eps_post, eps_pre, stream);
+    if (w_dtype == PLM_BF16 && out_dtype == PLM_BF16)
+        return post_pre_norm_launch<bf16, bf16>(x, delta, w_post, w_pre, out, n_rows, d, eps_post, eps_pre, stream);
+    return PLM_ERR_DTYPE;
+}
+
 // ------------------------------------------------ rows whose scale is still due
 // out[t, :] = bf16(x[t, :] * r[t]) with r[t] = 1 / sqrt(sum_p parts[p, t] / size + eps): what is left of
 // an RMSNorm whose weight a product's epilogue has already applied (x) and whose sums of squares it has

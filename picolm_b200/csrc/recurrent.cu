@@ -130,6 +130,15 @@ extern "C" int plm_causal_conv(const void* u, int dtype, long ldu, const float* 
 #define DECAY_STEP 1
 #define DECAY_SIGMOID 2
 
+// What a launch of the scan kernel does with the tokens of its segment:
+//   SCAN_WHOLE  one segment per sequence: from the cache's state, writes y and the state (decode steps, short prompts)
+//   SCAN_LOCAL  from zero, no y: leaves the segment's own contribution to the state and the product of its decays
+//   SCAN_FINAL  from the state at the segment's start (put together by scan_combine_kernel), writes y; the last
+//               segment of a sequence writes the cache's state
+#define SCAN_WHOLE 0
+#define SCAN_LOCAL 1
+#define SCAN_FINAL 2
+
 struct ScanArgs {
     const void *q, *k, *v, *raw;          // [T, groups * N], [T, groups * N], [T, H * P], the decay's raw values
     long ldq, ldk, ldv, ldraw;            // row strides in elements
@@ -141,15 +150,18 @@ struct ScanArgs {
     long ldy;
     const int *seq_start, *seq_slot;
     int n_seqs, H, N, P, heads_per_group;
+    int seg_len, max_segs;                // tokens per segment; segments of the longest sequence
+    float *seg_state, *seg_decay;         // [seq][segment][H][N][P] and [seq][segment][H][N]
 };
 
-// One block per (sequence, head, tile of 32 value columns).  A warp holds 8 columns; the N rows of a column's
-// state are dealt to 4 lanes (NS consecutive rows each, in registers).  The tokens of the sequence are taken in
-// order, TC at a time: the block first brings their q, k, decay and v to shared memory as fp32 (the
-// exponentials are taken there, once per token and channel), then every thread steps its rows through them.
-template <typename T, int NS, int MODE>
+// One block per (sequence, head, tile of 32 value columns, segment).  A warp holds 8 columns, two groups of 4; the
+// N rows of a column group's state are dealt to 16 lanes (NS consecutive rows each), so a thread keeps NS x 4
+// values of the state in registers.  The tokens are taken in order, TC at a time: the block first brings their q,
+// k, decay and v to shared memory as fp32 (the exponentials are taken there, once per token and channel), then every
+// thread steps its piece of the state through them; y's sum over the rows goes through the 16 lanes by shuffles.
+template <typename T, int NS, int MODE, int PASS>
 __global__ void __launch_bounds__(SCAN_THREADS) linear_scan_kernel(const ScanArgs a, int TC) {
-    constexpr int ROW = NS + 4;                           // padded so that the four lanes' float4 reads hit different banks
+    constexpr int ROW = NS == 4 ? 4 : NS + 4;             // padded so that a quarter warp's float4 reads hit different banks
     constexpr bool PER_CHANNEL = MODE == DECAY_SIGMOID;
     extern __shared__ __align__(16) float smem[];
     pdl_launch_dependents();
@@ -158,41 +170,55 @@ __global__ void __launch_bounds__(SCAN_THREADS) linear_scan_kernel(const ScanArg
     const int ptile = bid % ptiles;
     bid /= ptiles;
     const int h = bid % a.H, b = bid / a.H;
+    const int seg = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int npart = lane >> 3, pl = (warp << 3) + (lane & 7);
+    const int npart = lane & 15, pg = lane >> 4;
+    const int pl = (warp << 3) + (pg << 2);               // first of this thread's 4 columns within the tile
     const int p = ptile * SCAN_PTILE + pl;
     const int g = h / a.heads_per_group;
     const int N = a.N, P = a.P;
-    float* qs = smem;                                     // [TC][4][ROW]
-    float* ks = qs + (long)TC * 4 * ROW;
-    float* ds = ks + (long)TC * 4 * ROW;                  // per channel: [TC][4][ROW]; per head: [TC] decay, [TC] scale of v
-    float* vs = ds + (PER_CHANNEL ? (long)TC * 4 * ROW : 2L * TC);    // [TC][SCAN_PTILE]
+    float* qs = smem;                                     // [TC][16][ROW]
+    float* ks = qs + (long)TC * 16 * ROW;
+    float* ds = ks + (long)TC * 16 * ROW;                 // per channel: [TC][16][ROW]; per head: [TC] decay, [TC] scale of v
+    float* vs = ds + (PER_CHANNEL ? (long)TC * 16 * ROW : (long)((2 * TC + 3) & ~3));    // [TC][SCAN_PTILE]
     const T* q = (const T*)a.q;
     const T* k = (const T*)a.k;
     const T* v = (const T*)a.v;
     const T* raw = (const T*)a.raw;
     pdl_wait();
-    const int t0 = a.seq_start[b], t1 = a.seq_start[b + 1];
+    const int s0 = a.seq_start[b], s1 = a.seq_start[b + 1];
+    const int n_segs = PASS == SCAN_WHOLE ? 1 : (s1 - s0 + a.seg_len - 1) / a.seg_len;
+    if (PASS == SCAN_LOCAL && seg >= n_segs - 1) return;  // nobody needs what the last segment adds by itself
+    if (PASS == SCAN_FINAL && seg >= n_segs) return;
+    const int t0 = PASS == SCAN_WHOLE ? s0 : s0 + seg * a.seg_len;
+    const int t1 = PASS == SCAN_WHOLE ? s1 : min(s1, t0 + a.seg_len);
     float* st = a.state + (long)a.seq_slot[b] * a.state_stride + (long)h * N * P;
-    float S[NS];
+    float* sg = PASS == SCAN_WHOLE ? nullptr : a.seg_state + (((long)b * a.max_segs + seg) * a.H + h) * N * P;
+    const float* init = PASS == SCAN_WHOLE ? st : PASS == SCAN_FINAL ? sg : nullptr;
+    float S[NS][4];
+    float dprod[PER_CHANNEL ? NS : 1];
+#pragma unroll
+    for (int i = 0; i < (PER_CHANNEL ? NS : 1); ++i) dprod[i] = 1.f;
 #pragma unroll
     for (int i = 0; i < NS; ++i) {
         const int n = npart * NS + i;
-        S[i] = (n < N && p < P) ? st[(long)n * P + p] : 0.f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) S[i][j] = (init && n < N && p + j < P) ? init[(long)n * P + p + j] : 0.f;
     }
     const float skip = a.skip ? a.skip[h] : 0.f;
     for (int base = t0; base < t1; base += TC) {
         const int nt = min(TC, t1 - base);
         __syncthreads();
-        for (int idx = threadIdx.x; idx < nt * 4 * NS; idx += SCAN_THREADS) {
-            const int tt = idx / (4 * NS), n = idx % (4 * NS);
-            const int at = (tt * 4 + n / NS) * ROW + n % NS;
+#pragma unroll 2
+        for (int idx = threadIdx.x; idx < nt * 16 * NS; idx += SCAN_THREADS) {
+            const int tt = idx / (16 * NS), n = idx % (16 * NS);
+            const int at = (tt * 16 + n / NS) * ROW + n % NS;
             const long row = base + tt;
             const bool in = n < N;
-            qs[at] = in ? to_f32<T>(q[row * a.ldq + (long)g * N + n]) * a.q_scale : 0.f;
+            if (PASS != SCAN_LOCAL) qs[at] = in ? to_f32<T>(q[row * a.ldq + (long)g * N + n]) * a.q_scale : 0.f;
             ks[at] = in ? to_f32<T>(k[row * a.ldk + (long)g * N + n]) : 0.f;
             if (PER_CHANNEL)
-                ds[at] = in ? expf(log_sigmoid_f(to_f32<T>(raw[row * a.ldraw + (long)h * N + n]) + a.p0[(long)h * N + n]) * a.power) : 0.f;
+                ds[at] = in ? expf(log_sigmoid_f(to_f32<T>(raw[row * a.ldraw + (long)h * N + n]) + a.p0[(long)h * N + n]) * a.power) : 1.f;
         }
         if (!PER_CHANNEL) {
             for (int tt = threadIdx.x; tt < nt; tt += SCAN_THREADS) {
@@ -207,79 +233,175 @@ __global__ void __launch_bounds__(SCAN_THREADS) linear_scan_kernel(const ScanArg
         }
         __syncthreads();
         for (int tt = 0; tt < nt; ++tt) {
-            const float x = vs[tt * SCAN_PTILE + pl];
-            const float vv = PER_CHANNEL ? x : ds[TC + tt] * x;
+            const float4 x = *(const float4*)(vs + tt * SCAN_PTILE + pl);
+            const float vsc = PER_CHANNEL ? 1.f : ds[TC + tt];
+            const float4 vv = make_float4(vsc * x.x, vsc * x.y, vsc * x.z, vsc * x.w);
             const float dh = PER_CHANNEL ? 0.f : ds[tt];
-            const float4* q4 = (const float4*)(qs + (tt * 4 + npart) * ROW);
-            const float4* k4 = (const float4*)(ks + (tt * 4 + npart) * ROW);
-            const float4* d4 = (const float4*)(ds + (tt * 4 + npart) * ROW);
-            float acc0 = 0.f, acc1 = 0.f;
+            if (!PER_CHANNEL) dprod[0] *= dh;
+            const float4* q4 = (const float4*)(qs + (tt * 16 + npart) * ROW);
+            const float4* k4 = (const float4*)(ks + (tt * 16 + npart) * ROW);
+            const float4* d4 = (const float4*)(ds + (tt * 16 + npart) * ROW);
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-            for (int i = 0; i < NS / 4; ++i) {
-                const float4 qq = q4[i], kk = k4[i];
-                float4 dd;
-                if (PER_CHANNEL) dd = d4[i];
-                else dd = make_float4(dh, dh, dh, dh);
-                S[4 * i + 0] = fmaf(dd.x, S[4 * i + 0], kk.x * vv);
-                S[4 * i + 1] = fmaf(dd.y, S[4 * i + 1], kk.y * vv);
-                S[4 * i + 2] = fmaf(dd.z, S[4 * i + 2], kk.z * vv);
-                S[4 * i + 3] = fmaf(dd.w, S[4 * i + 3], kk.w * vv);
-                acc0 = fmaf(S[4 * i + 0], qq.x, acc0);
-                acc1 = fmaf(S[4 * i + 1], qq.y, acc1);
-                acc0 = fmaf(S[4 * i + 2], qq.z, acc0);
-                acc1 = fmaf(S[4 * i + 3], qq.w, acc1);
+            for (int i4 = 0; i4 < NS / 4; ++i4) {
+                const float4 kk = k4[i4];
+                float4 qq = make_float4(0.f, 0.f, 0.f, 0.f), dd = make_float4(dh, dh, dh, dh);
+                if (PASS != SCAN_LOCAL) qq = q4[i4];
+                if (PER_CHANNEL) dd = d4[i4];
+                const float kr[4] = {kk.x, kk.y, kk.z, kk.w}, qr[4] = {qq.x, qq.y, qq.z, qq.w}, dr[4] = {dd.x, dd.y, dd.z, dd.w};
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    float* Sr = S[4 * i4 + r];
+                    if (PER_CHANNEL) dprod[4 * i4 + r] *= dr[r];
+                    Sr[0] = fmaf(dr[r], Sr[0], kr[r] * vv.x);
+                    Sr[1] = fmaf(dr[r], Sr[1], kr[r] * vv.y);
+                    Sr[2] = fmaf(dr[r], Sr[2], kr[r] * vv.z);
+                    Sr[3] = fmaf(dr[r], Sr[3], kr[r] * vv.w);
+                    if (PASS != SCAN_LOCAL) {
+                        acc.x = fmaf(Sr[0], qr[r], acc.x);
+                        acc.y = fmaf(Sr[1], qr[r], acc.y);
+                        acc.z = fmaf(Sr[2], qr[r], acc.z);
+                        acc.w = fmaf(Sr[3], qr[r], acc.w);
+                    }
+                }
             }
-            float acc = acc0 + acc1;
-            acc += __shfl_xor_sync(0xffffffffu, acc, 8);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 16);
-            if (npart == 0 && p < P) a.y[(long)(base + tt) * a.ldy + (long)h * P + p] = fmaf(skip, x, acc);
+            if (PASS != SCAN_LOCAL) {
+#pragma unroll
+                for (int o = 1; o < 16; o <<= 1) {
+                    acc.x += __shfl_xor_sync(0xffffffffu, acc.x, o);
+                    acc.y += __shfl_xor_sync(0xffffffffu, acc.y, o);
+                    acc.z += __shfl_xor_sync(0xffffffffu, acc.z, o);
+                    acc.w += __shfl_xor_sync(0xffffffffu, acc.w, o);
+                }
+                if (npart == 0) {
+                    float* yr = a.y + (long)(base + tt) * a.ldy + (long)h * P + p;
+                    const float out[4] = {fmaf(skip, x.x, acc.x), fmaf(skip, x.y, acc.y), fmaf(skip, x.z, acc.z), fmaf(skip, x.w, acc.w)};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        if (p + j < P) yr[j] = out[j];
+                }
+            }
         }
     }
+    float* dst = PASS == SCAN_LOCAL ? sg : (PASS == SCAN_WHOLE || seg == n_segs - 1) ? st : nullptr;
+    if (dst) {
 #pragma unroll
-    for (int i = 0; i < NS; ++i) {
-        const int n = npart * NS + i;
-        if (n < N && p < P) st[(long)n * P + p] = S[i];
+        for (int i = 0; i < NS; ++i) {
+            const int n = npart * NS + i;
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (n < N && p + j < P) dst[(long)n * P + p + j] = S[i][j];
+        }
+    }
+    if (PASS == SCAN_LOCAL && ptile == 0 && warp == 0 && pg == 0) {
+        float* dd = a.seg_decay + (((long)b * a.max_segs + seg) * a.H + h) * N;
+#pragma unroll
+        for (int i = 0; i < NS; ++i) {
+            const int n = npart * NS + i;
+            if (n < N) dd[n] = PER_CHANNEL ? dprod[PER_CHANNEL ? i : 0] : dprod[0];
+        }
     }
 }
 
-template <typename T, int NS>
-static cudaError_t scan_launch(const ScanArgs& a, int mode, cudaStream_t stream) {
-    const int ROW = NS + 4;
-    // tokens per pass: as many as fit into about 36 KB of shared memory, 16 at most
-    const long per_token = (mode == DECAY_SIGMOID ? 3L : 2L) * 4 * ROW + SCAN_PTILE + 2;
-    int TC = (int)((36 * 1024 / 4) / per_token);
-    TC = TC > 16 ? 16 : TC < 1 ? 1 : TC;
-    const size_t smem = (size_t)(per_token * TC) * sizeof(float);
+// Between the two passes over the segments: the state at the start of every segment, from the cache's state and
+// what the segments before it add: S_in[0] = state, S_in[c + 1] = decay[c] * S_in[c] + local[c].  One thread per
+// element of a sequence's state; S_in[c] takes local[c]'s place.
+__global__ void scan_combine_kernel(const ScanArgs a) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long per_seq = (long)a.H * a.N * a.P;
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= per_seq * a.n_seqs) return;
+    const int b = (int)(idx / per_seq);
+    const long e = idx % per_seq;
+    const long hn = e / a.P;
+    const int n_segs = (a.seq_start[b + 1] - a.seq_start[b] + a.seg_len - 1) / a.seg_len;
+    float S = a.state[(long)a.seq_slot[b] * a.state_stride + e];
+    float* sg = a.seg_state + (long)b * a.max_segs * per_seq + e;
+    const float* dd = a.seg_decay + (long)b * a.max_segs * a.H * a.N + hn;
+    for (int c = 0; c < n_segs; ++c) {
+        const float local = c < n_segs - 1 ? sg[(long)c * per_seq] : 0.f;
+        sg[(long)c * per_seq] = S;
+        if (c < n_segs - 1) S = fmaf(dd[(long)c * a.H * a.N], S, local);
+    }
+}
+
+template <int NS>
+static size_t scan_smem(int mode, int* TC) {
+    const int ROW = NS == 4 ? 4 : NS + 4;
+    // tokens per pass: as many as fit into about 40 KB of shared memory, 16 at most
+    const long per_token = (mode == DECAY_SIGMOID ? 3L : 2L) * 16 * ROW + SCAN_PTILE + (mode == DECAY_SIGMOID ? 0 : 2);
+    int tc = (int)((40 * 1024 / 4 - 4) / per_token);
+    tc = tc > 16 ? 16 : tc < 1 ? 1 : tc;
+    *TC = tc;
+    return (size_t)(per_token * tc + 4) * sizeof(float);
+}
+
+template <typename T, int NS, int MODE>
+static cudaError_t scan_launch(const ScanArgs& a, cudaStream_t stream) {
+    int TC;
+    const size_t smem = scan_smem<NS>(MODE, &TC);
     const int ptiles = (a.P + SCAN_PTILE - 1) / SCAN_PTILE;
-    const dim3 grid((unsigned)((long)a.n_seqs * a.H * ptiles));
-    if (mode == DECAY_SIGMOID)
-        return launch_pdl(linear_scan_kernel<T, NS, DECAY_SIGMOID>, grid, dim3(SCAN_THREADS), smem, stream, a, TC);
-    return launch_pdl(linear_scan_kernel<T, NS, DECAY_STEP>, grid, dim3(SCAN_THREADS), smem, stream, a, TC);
+    const unsigned blocks = (unsigned)((long)a.n_seqs * a.H * ptiles);
+    if (a.max_segs <= 1)
+        return launch_pdl(linear_scan_kernel<T, NS, MODE, SCAN_WHOLE>, dim3(blocks), dim3(SCAN_THREADS), smem, stream, a, TC);
+    cudaError_t e = launch_pdl(linear_scan_kernel<T, NS, MODE, SCAN_LOCAL>, dim3(blocks, a.max_segs - 1), dim3(SCAN_THREADS), smem,
+                               stream, a, TC);
+    if (e != cudaSuccess) return e;
+    const long elems = (long)a.n_seqs * a.H * a.N * a.P;
+    e = launch_pdl(scan_combine_kernel, dim3((unsigned)((elems + 255) / 256)), dim3(256), 0, stream, a);
+    if (e != cudaSuccess) return e;
+    return launch_pdl(linear_scan_kernel<T, NS, MODE, SCAN_FINAL>, dim3(blocks, a.max_segs), dim3(SCAN_THREADS), smem, stream, a, TC);
 }
 
 template <typename T>
 static int scan_dispatch(const ScanArgs& a, int mode, cudaStream_t stream) {
-    const int ns = (a.N + 3) / 4;
+    const int ns = (a.N + 15) / 16;
     cudaError_t e;
-    if (ns <= 4) e = scan_launch<T, 4>(a, mode, stream);
-    else if (ns <= 8) e = scan_launch<T, 8>(a, mode, stream);
-    else if (ns <= 16) e = scan_launch<T, 16>(a, mode, stream);
-    else if (ns <= 32) e = scan_launch<T, 32>(a, mode, stream);
-    else if (ns <= 64) e = scan_launch<T, 64>(a, mode, stream);
+#define SCAN_NS(NS_) (mode == DECAY_SIGMOID ? scan_launch<T, NS_, DECAY_SIGMOID>(a, stream) : scan_launch<T, NS_, DECAY_STEP>(a, stream))
+    if (ns <= 4) e = SCAN_NS(4);
+    else if (ns <= 8) e = SCAN_NS(8);
+    else if (ns <= 16) e = SCAN_NS(16);
     else return PLM_ERR_UNSUPPORTED;
+#undef SCAN_NS
     return plm_status_of(e);
+}
+
+// How a step whose longest sequence brings `max_new` tokens is cut: out[0] tokens per segment, out[1] segments of the
+// longest sequence (1: one pass from the cache's state, no scratch memory).  Segments are worth their second pass
+// when the sequences alone leave most of the GPU idle; there are as many as give every SM a few blocks, each of at
+// least 64 tokens, and no more than keep the scratch memory under 1 GiB.
+extern "C" int plm_linear_scan_plan(int n_seqs, int H, int N, int P, int max_new, int* out) {
+    out[0] = max_new > 0 ? max_new : 1;
+    out[1] = 1;
+    if (n_seqs <= 0 || H <= 0 || N <= 0 || P <= 0) return PLM_ERR_SHAPE;
+    if (max_new < 192) return PLM_OK;
+    const long blocks = (long)n_seqs * H * ((P + SCAN_PTILE - 1) / SCAN_PTILE);
+    long segs = (6L * PLM_SM_COUNT + blocks - 1) / blocks;
+    const long most = max_new / 64;
+    if (segs > most) segs = most;
+    const long state_bytes = (long)n_seqs * H * N * (P + 1) * 4;
+    while (segs > 1 && segs * state_bytes > (1L << 30)) --segs;
+    if (segs <= 1) return PLM_OK;
+    int len = (int)((max_new + segs - 1) / segs);
+    len = (len + 15) / 16 * 16;
+    out[0] = len;
+    out[1] = (max_new + len - 1) / len;
+    return PLM_OK;
 }
 
 extern "C" int plm_linear_scan(const void* q, const void* k, const void* v, const void* raw, int dtype, long ldq, long ldk,
                                long ldv, long ldraw, int mode, const float* p0, const float* p1, const float* skip,
                                float q_scale, float power, float* state, long state_stride, float* y, long ldy,
                                const int* seq_start, const int* seq_slot, int n_seqs, int H, int N, int P,
-                               int heads_per_group, cudaStream_t stream) {
+                               int heads_per_group, int seg_len, int max_segs, float* seg_state, float* seg_decay,
+                               cudaStream_t stream) {
     if (n_seqs <= 0 || H <= 0 || N <= 0 || P <= 0 || heads_per_group <= 0) return PLM_ERR_SHAPE;
     if (mode != DECAY_STEP && mode != DECAY_SIGMOID) return PLM_ERR_UNSUPPORTED;
     if (mode == DECAY_STEP && !p1) return PLM_ERR_SHAPE;
     if (!p0) return PLM_ERR_SHAPE;
     if (N > 256) return PLM_ERR_UNSUPPORTED;
+    if (max_segs > 1 && (!seg_state || !seg_decay || seg_len <= 0 || max_segs > 65535)) return PLM_ERR_SHAPE;
     ScanArgs a;
     a.q = q, a.k = k, a.v = v, a.raw = raw;
     a.ldq = ldq, a.ldk = ldk, a.ldv = ldv, a.ldraw = ldraw;
@@ -289,6 +411,8 @@ extern "C" int plm_linear_scan(const void* q, const void* k, const void* v, cons
     a.y = y, a.ldy = ldy;
     a.seq_start = seq_start, a.seq_slot = seq_slot;
     a.n_seqs = n_seqs, a.H = H, a.N = N, a.P = P, a.heads_per_group = heads_per_group;
+    a.seg_len = seg_len, a.max_segs = max_segs < 1 ? 1 : max_segs;
+    a.seg_state = seg_state, a.seg_decay = seg_decay;
     if (dtype == PLM_F32) return scan_dispatch<float>(a, mode, stream);
     if (dtype == PLM_BF16) return scan_dispatch<bf16>(a, mode, stream);
     return PLM_ERR_DTYPE;
@@ -317,6 +441,7 @@ __global__ void gated_norm_kernel(const TI* __restrict__ x, long ldx, const TG* 
     float r = 1.f;
     if (do_norm) {
         float ss = 0.f;
+#pragma unroll 4
         for (int c = lane; c < group; c += 32) {
             float val = to_f32<TI>(xr[c]);
             if (gate_mode == 1) {
@@ -328,6 +453,7 @@ __global__ void gated_norm_kernel(const TI* __restrict__ x, long ldx, const TG* 
         ss = warp_sum(ss);
         r = 1.f / sqrtf(ss / (float)group + eps);
     }
+#pragma unroll 4
     for (int c = lane; c < group; c += 32) {
         float val = to_f32<TI>(xr[c]);
         float ga = 1.f;

@@ -109,11 +109,19 @@ __device__ __forceinline__ void tc_wait_ld_into(uint32_t* r) {
     for (int i = 0; i < 32; ++i) asm volatile("" : "+r"(r[i]));
 }
 
+// With -DPLM_GATE_GELU (a build variant of the libraries that have this epilogue) the activation is the tanh form of
+// GELU instead: 0.5 g (1 + tanh(y)) = g / (1 + e^(-2y)) with y = sqrt(2/pi) (g + 0.044715 g^3), so the same two
+// special-function instructions serve.
 __device__ __forceinline__ float swiglu_bf16(float g, float u) {
     g = __bfloat162float(__float2bfloat16_rn(g));
     u = __bfloat162float(__float2bfloat16_rn(u));
     float e;
+#ifdef PLM_GATE_GELU
+    const float y2 = 1.5957691216057308f * fmaf(0.044715f * g * g, g, g);            // 2 sqrt(2/pi) (g + 0.044715 g^3)
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(y2 * -1.4426950408889634f));
+#else
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(g * -1.4426950408889634f));
+#endif
     return __fdividef(g, 1.0f + e) * u;
 }
 

@@ -19,6 +19,7 @@ _vp, _i, _l, _f = ctypes.c_void_p, ctypes.c_int, ctypes.c_long, ctypes.c_float
 _SIGNATURES = {
     "plm_embed": [_vp, _vp, _i, _vp, _i, _i, _i, _vp],
     "plm_rmsnorm": [_vp, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _f, _vp],
+    "plm_post_pre_norm": [_vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _f, _f, _vp],
     "plm_swiglu": [_vp, _vp, _i, _i, _i, _i, _vp],
     "plm_rope_store": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
     "plm_gemm_tc_skinny": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _l, _l, _l, _vp, _vp],
@@ -48,7 +49,8 @@ _SIGNATURES = {
     "plm_decode_chain_scratch": [_i, _i, _i],
     "plm_causal_conv": [_vp, _i, _l, _vp, _vp, _vp, _l, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "plm_linear_scan": [_vp, _vp, _vp, _vp, _i, _l, _l, _l, _l, _i, _vp, _vp, _vp, _f, _f, _vp, _l, _vp, _l, _vp, _vp,
-                        _i, _i, _i, _i, _i, _vp],
+                        _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp],
+    "plm_linear_scan_plan": [_i, _i, _i, _i, _i, _vp],
     "plm_gated_norm": [_vp, _i, _l, _vp, _i, _l, _vp, _i, _vp, _i, _l, _i, _i, _i, _f, _i, _i, _i, _vp],
     "plm_head_linear": [_vp, _i, _l, _vp, _vp, _l, _vp, _l, _i, _i, _i, _i, _vp],
     "plm_store_rows_paged": [_vp, _i, _l, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],

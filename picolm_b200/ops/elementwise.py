@@ -57,6 +57,30 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.
     return out
 
 
+def post_pre_norm_supported(x: torch.Tensor, delta, w_post: torch.Tensor, w_pre: torch.Tensor) -> bool:
+    """Whether `post_pre_norm` takes this case: float32 stream and delta of one shape, rows of a multiple of 4 and at
+    most 16,384 columns, two norm weights of one type."""
+    return (isinstance(delta, torch.Tensor) and delta.dtype == torch.float32 and x.dtype == torch.float32
+            and delta.shape == x.shape and x.is_contiguous() and delta.is_contiguous() and x.shape[1] % 4 == 0
+            and x.shape[1] <= 16384 and w_post.dtype == w_pre.dtype and w_post.shape == w_pre.shape == (x.shape[1],)
+            and x.data_ptr() % 16 == 0 and delta.data_ptr() % 16 == 0)
+
+
+def post_pre_norm(x: torch.Tensor, delta: torch.Tensor, w_post: torch.Tensor, eps_post: float, w_pre: torch.Tensor,
+                  eps_pre: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """x += RMSNorm(delta; w_post) in place on the fp32 stream, and RMSNorm(x; w_pre) of the new x as [T, d] of
+    `out_dtype`: a sublayer's closing norm, the residual add and the next sublayer's opening norm in one kernel."""
+    _dev(x, "x"), _dev(delta, "delta"), _dev(w_post, "w_post"), _dev(w_pre, "w_pre")
+    if not post_pre_norm_supported(x, delta, w_post, w_pre):
+        raise KernelError("post_pre_norm: not a case the fused kernel takes")
+    T, d = x.shape
+    out = torch.empty((T, d), dtype=out_dtype, device=x.device)
+    _check(_fn("elementwise", "plm_post_pre_norm")(
+        _p(x), _p(delta), _p(w_post), _p(w_pre), _dt(w_pre, "w_pre"), _p(out), _dt(out, "out"), T, d, float(eps_post),
+        float(eps_pre), _stream()), f"post_pre_norm rows={T} d={d}", nbytes=T * d * (12 + out.element_size()))
+    return out
+
+
 def gather_rows(x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
     """x[rows] for a 2-D `x` with contiguous rows and int32 `rows` on the device: [len(rows), x.shape[1]]."""
     _i32(rows, "rows")

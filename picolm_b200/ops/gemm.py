@@ -49,8 +49,18 @@ def gemm_tc_supported(a: torch.Tensor, w: torch.Tensor) -> bool:
             and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
+def _gated_library(name: str, flags: tuple, activation: str):
+    """The build of a tensor-core library whose gated epilogue applies `activation` ("silu": the plain build;
+    "gelu_tanh": the variant compiled with -DPLM_GATE_GELU)."""
+    if activation == "silu":
+        return name, flags
+    if activation != "gelu_tanh":
+        raise KernelError(f"the gated epilogue knows silu and gelu_tanh, not {activation!r}")
+    return (name + "_gelu" if "@" in name else name + "@gelu"), tuple(flags) + ("-DPLM_GATE_GELU",)
+
+
 def gemm_tc_skinny(a, w: torch.Tensor, out_dtype: torch.dtype, swiglu: bool = False,
-                   out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                   out: Optional[torch.Tensor] = None, activation: str = "silu") -> torch.Tensor:
     """The decode-shaped tensor-core product: a [M <= 64, K] @ w [N, K]^T with the weights on the MMA's 128
     rows and K split over a thread-block cluster whose CTAs add their partial tiles up through distributed
     shared memory.  With `swiglu`, w holds tiles of 64 gate rows followed by their 64 up rows (see
@@ -74,13 +84,14 @@ def gemm_tc_skinny(a, w: torch.Tensor, out_dtype: torch.dtype, swiglu: bool = Fa
     n_out = N // 2 if swiglu else N
     if out is None:
         out = torch.empty((M, n_out), dtype=out_dtype, device=a.device)
+    lib, lib_flags = _gated_library("gemm_tc_skinny", (), activation if swiglu else "silu")
     if scaled is not None:
-        _check(_fn("gemm_tc_skinny", "plm_gemm_tc_skinny_scaled")(
+        _check(_fn(lib, "plm_gemm_tc_skinny_scaled", lib_flags)(
             _p(a), _p(w), _p(out), 1 if swiglu else 0, M, N, K, K, K, n_out, _p(scaled.parts), scaled.parts.shape[0],
             scaled.parts.shape[1], scaled.size, float(scaled.eps), _p(status_word(a.device)), _stream()),
             f"gemm_tc_skinny{'_swiglu' if swiglu else ''}_scaled {M}x{N}x{K}", **_work(a, w, out))
         return out
-    _check(_fn("gemm_tc_skinny", "plm_gemm_tc_skinny")(
+    _check(_fn(lib, "plm_gemm_tc_skinny", lib_flags)(
         _p(a), _p(w), _p(out), _dt(out, "out"), 1 if swiglu else 0, M, N, K, K, K, n_out,
         _p(status_word(a.device)), _stream()), f"gemm_tc_skinny{'_swiglu' if swiglu else ''} {M}x{N}x{K}", **_work(a, w, out))
     return out
@@ -202,7 +213,8 @@ def linear_residual_norm(pending: PendingLinear, x: torch.Tensor, norm_weight: t
 
 
 def gemm_tc_wide(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, swiglu: bool = False,
-                 out: Optional[torch.Tensor] = None, pair: bool = False, add: bool = False) -> torch.Tensor:
+                 out: Optional[torch.Tensor] = None, pair: bool = False, add: bool = False,
+                 activation: str = "silu") -> torch.Tensor:
     """The prompt-shaped tensor-core product: a [M > 64, K] @ w [N, K]^T by a persistent tcgen05 kernel
     (one CTA per SM, two accumulators in tensor memory so that a tile's epilogue overlaps the next
     tile's main loop; where the tiles do not fill one round over the SMs and K is long, the K blocks of all
@@ -230,11 +242,13 @@ def gemm_tc_wide(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, swigl
     work = _work(a, w, out, extra=out.numel() * 4 if add else 0)
     # Shapes whose tiles leave most SMs idle walk K as one stream: that code is in a build variant of the library
     # (compiled when the first such shape comes), with a workspace; everything else runs the plain build.
-    STREAM_LIB = ("gemm_tc_wide@stream", ("-DPLM_WIDE_STREAM",))
+    act = activation if swiglu else "silu"
+    STREAM_LIB = _gated_library("gemm_tc_wide@stream", ("-DPLM_WIDE_STREAM",), act)
+    PLAIN_LIB = _gated_library("gemm_tc_wide", (), act)
     if pair:
         streamed = K % 64 == 0 and stream_space_enabled() and _pair_streamed(M, N, K) > 0
         parts, flags, slots = stream_space(a.device) if streamed else (None, None, 0)
-        lib = STREAM_LIB if streamed else ("gemm_tc_wide", ())
+        lib = STREAM_LIB if streamed else PLAIN_LIB
         _check(_fn(lib[0], "plm_gemm_tc_pair_space", lib[1])(
             _p(a), _p(w), _p(out), _dt(out, "out"), epilogue, M, N, K, K, K, n_out, _p(parts), _p(flags), slots,
             _p(status_word(a.device)), _stream()), "gemm_tc_pair" + (" (stream)" if streamed else "") + name, **work)
@@ -250,7 +264,7 @@ def gemm_tc_wide(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, swigl
         kernels = 2
     streamed = how[2] > 0
     parts, flags, slots = stream_space(a.device) if streamed else (None, None, 0)
-    lib = STREAM_LIB if streamed else ("gemm_tc_wide", ())
+    lib = STREAM_LIB if streamed else PLAIN_LIB
     _check(_fn(lib[0], "plm_gemm_tc_wide_space", lib[1])(
         _p(a), _p(w), _p(out), _dt(out, "out"), epilogue, M, N, K, K, K, n_out, _p(scratch), _p(parts), _p(flags), slots,
         _p(status_word(a.device)), _stream()), "gemm_tc_wide" + (" (stream)" if streamed else "") + name, kernels=kernels, **work)
@@ -311,12 +325,13 @@ def pair_pays(m: int, n: int, k: int = 0, epilogue: int = 0) -> bool:
     return _pair_streamed(m, n, k) > 0
 
 
-def linear_swiglu(a, w_gate_up: torch.Tensor, defer: bool = False):
+def linear_swiglu(a, w_gate_up: torch.Tensor, defer: bool = False, activation: str = "silu"):
     """silu(a @ gate^T) * (a @ up^T) with `w_gate_up` from `interleave_gate_up`: one tensor-core product
-    whose epilogue applies the activation; [M, F] in bfloat16.  `a` may be `ScaledRows`.  With `defer` (the
+    whose epilogue applies the activation ("silu", or "gelu_tanh" from a build variant of the same kernels); [M, F] in
+    bfloat16.  `a` may be `ScaledRows`.  With `defer` (the
     caller hands the result to `linear(..., defer=True)` and nowhere else) the result may be `LazyRows`."""
     if isinstance(a, ScaledRows) and a.chain is not None and a.chain.pending:
-        if gemm_tc_supported(a.x, w_gate_up) and w_gate_up.shape[0] % 128 == 0:
+        if activation == "silu" and gemm_tc_supported(a.x, w_gate_up) and w_gate_up.shape[0] % 128 == 0:
             ch = a.chain
             rows = ch.add_swiglu(w_gate_up, a.parts, a.size, a.eps)
             if defer:
@@ -333,8 +348,8 @@ def linear_swiglu(a, w_gate_up: torch.Tensor, defer: bool = False):
     if not gemm_tc_supported(x, w_gate_up) or N % 128:
         raise KernelError("linear_swiglu: needs bfloat16 operands the tensor-core kernel takes and N % 128 == 0")
     if M <= 64:
-        return gemm_tc_skinny(a, w_gate_up, torch.bfloat16, swiglu=True)
-    return gemm_tc_wide(a, w_gate_up, torch.bfloat16, swiglu=True, pair=pair_pays(M, N, K, 1))
+        return gemm_tc_skinny(a, w_gate_up, torch.bfloat16, swiglu=True, activation=activation)
+    return gemm_tc_wide(a, w_gate_up, torch.bfloat16, swiglu=True, pair=pair_pays(M, N, K, 1), activation=activation)
 
 
 def linear(a, w: torch.Tensor, out_dtype: torch.dtype, defer: bool = False):

@@ -92,13 +92,40 @@ def linear_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, raw: torch.Te
     if state.dtype != torch.float32 or state.shape[1] < H * N * P:
         raise KernelError("linear_scan: the state must be float32 with heads * key_dim * value_dim values a row")
     y = torch.empty((T, H * P), dtype=torch.float32, device=v.device)
+    # Long prompts are cut into segments that run side by side: a first pass leaves what each segment adds to the
+    # state, a small kernel chains those into the state at every segment's start, a second pass gives y.
+    seg_len, n_segs = scan_plan(step.n_seqs, H, N, P, step.max_new)
+    seg_state = seg_decay = None
+    if n_segs > 1:
+        seg_state = torch.empty((step.n_seqs, n_segs, H * N * P), dtype=torch.float32, device=v.device)
+        seg_decay = torch.empty((step.n_seqs, n_segs, H * N), dtype=torch.float32, device=v.device)
     _check(_fn("recurrent", "plm_linear_scan")(
         _p(q), _p(k), _p(v), _p(raw), _dt(v, "v"), ldq, ldk, ldv, ldr, mode, _p(p0), _p(p1), _p(skip), float(q_scale),
         float(power), _p(state), lds, _p(y), H * P, _p(step.seq_start), _p(step.seq_slot), step.n_seqs, H, N, P,
-        heads_per_group, _stream()), f"linear_scan T={T} H={H} N={N} P={P}",
+        heads_per_group, seg_len, n_segs, _p(seg_state), _p(seg_decay), _stream()),
+        f"linear_scan T={T} H={H} N={N} P={P}" + (f" in {n_segs} segments" if n_segs > 1 else ""),
+        kernels=3 if n_segs > 1 else 1,
         nbytes=T * (2 * G * N + H * P) * v.element_size() + T * H * P * 4 + 2 * step.n_seqs * H * N * P * 4,
-        flops=6 * T * H * N * P)
+        flops=(10 if n_segs > 1 else 6) * T * H * N * P)
     return y
+
+
+_plans = {}
+
+
+def scan_plan(n_seqs: int, heads: int, key_dim: int, value_dim: int, max_new: int):
+    """(tokens per segment, segments of the longest sequence) of `linear_scan` for a step whose longest sequence brings
+    `max_new` tokens; one segment means one pass from the cache's state."""
+    key = (n_seqs, heads, key_dim, value_dim, max_new)
+    plan = _plans.get(key)
+    if plan is None:
+        import ctypes
+        out = (ctypes.c_int * 2)()
+        _fn("recurrent", "plm_linear_scan_plan")(n_seqs, heads, key_dim, value_dim, int(max_new), ctypes.cast(out, ctypes.c_void_p))
+        if len(_plans) > 4096:
+            _plans.clear()
+        plan = _plans[key] = (out[0], out[1])
+    return plan
 
 
 GATE_NONE, GATE_BEFORE_NORM, GATE_AFTER_NORM = 0, 1, 2

@@ -20,6 +20,7 @@ from typing import List
 
 from ..config.spec import LayerSpec, PartSpec
 from .base import Part, build_part, register_part
+from .stream import PostNormed
 
 
 class Arrangement(Part):
@@ -121,11 +122,12 @@ class SandwichNormBlock(Arrangement):
             stream.pending = delta
             stream.narrow(keep_rows)
             delta = stream.pending
-        stream.pending = self.mixer_post_norm.normalize(delta)
+        # the closing norms are left to the norm that reads the stream next: it does them with the add and its own work
+        stream.pending = PostNormed(delta, self.mixer_post_norm)
         if "feed_forward" not in self.named:
             return
         h = self.feed_forward_norm.forward(stream)
-        stream.pending = self.feed_forward_post_norm.normalize(self._rows(self.feed_forward.forward(h, step)))
+        stream.pending = PostNormed(self._rows(self.feed_forward.forward(h, step)), self.feed_forward_post_norm)
 
 
 def sandwich_norm_layer(prefix: str, mixer: PartSpec, mixer_norm: PartSpec, mixer_post_norm: PartSpec,

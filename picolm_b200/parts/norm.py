@@ -10,7 +10,7 @@ import torch
 
 from .. import ops
 from .base import Part, WeightSpec, register_part
-from .stream import ResidualStream
+from .stream import PostNormed, ResidualStream
 
 
 @register_part("norm", "rmsnorm")
@@ -43,6 +43,14 @@ class RMSNorm(Part):
         With `defer_scale` (the caller hands the result to products only) a pending product runs
         with the add, this norm's weight and the sums of squares in its epilogue, and the result is
         `ops.ScaledRows`: the product that takes it applies the scale."""
+        p = stream.pending
+        if isinstance(p, PostNormed):
+            # a sublayer's result that wants a norm of its own before the add: both norms and the add in one kernel
+            if rows is None and ops.post_pre_norm_supported(stream.x, p.delta, p.norm.weight, self.weight):
+                stream.pending = None
+                return ops.post_pre_norm(stream.x, p.delta, p.norm.weight, p.norm.params["eps"], self.weight,
+                                         self.params["eps"], self.runtime.dtype)
+            stream.pending = p.compute()
         if (defer_scale and rows is None
                 and ops.residual_norm_supported(stream.pending, stream.x, self.weight)):
             h = ops.linear_residual_norm(stream.pending, stream.x, self.weight, self.params["eps"])

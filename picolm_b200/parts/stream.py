@@ -9,6 +9,25 @@ from typing import Optional
 import torch
 
 
+class PostNormed:
+    """A sublayer's float32 result that is still to be normalised (by `norm`, an RMSNorm part) before it is added to
+    the stream: the next norm over the stream may do both in one kernel; anything else calls `compute()`."""
+    __slots__ = ("delta", "norm")
+
+    def __init__(self, delta: torch.Tensor, norm):
+        self.delta, self.norm = delta, norm
+
+    @property
+    def shape(self):
+        return self.delta.shape
+
+    def compute(self) -> torch.Tensor:
+        return self.norm.normalize(self.delta)
+
+    def adds_in_place(self, x: torch.Tensor) -> bool:
+        return False
+
+
 @dataclass
 class ResidualStream:
     x: torch.Tensor                              # fp32 [T, d]
@@ -23,7 +42,9 @@ class ResidualStream:
         self.x = ops.gather_rows(self.x, rows)
         p = self.pending
         if p is not None:
-            if isinstance(p, ops.PendingLinear):
+            if isinstance(p, PostNormed):
+                self.pending = PostNormed(ops.gather_rows(p.delta, rows), p.norm)
+            elif isinstance(p, ops.PendingLinear):
                 a = p.a.materialize() if isinstance(p.a, ops.LazyRows) else p.a
                 self.pending = ops.PendingLinear(ops.gather_rows(a, rows), p.w)
             else:

@@ -91,7 +91,7 @@ class _Step:
         for n in lens:
             offs.append(offs[-1] + n)
         i32 = dict(dtype=torch.int32, device=dev)
-        self.n_seqs, self.n_tokens = len(lens), offs[-1]
+        self.n_seqs, self.n_tokens, self.max_new = len(lens), offs[-1], max(lens)
         self.is_decode = all(n == 1 for n in lens)
         self.seq_start = torch.tensor(offs, **i32)
         self.seq_slot = torch.tensor(slots, **i32)
@@ -131,17 +131,20 @@ def test_causal_conv_kernel(dtype, taps):
 
 
 @pytest.mark.parametrize("mode", ["step", "sigmoid"])
-@pytest.mark.parametrize("N,P_,H,hpg", [(8, 12, 6, 2), (5, 33, 2, 1), (48, 64, 4, 4), (130, 8, 1, 1)])
-def test_linear_scan_kernel(mode, N, P_, H, hpg):
+@pytest.mark.parametrize("N,P_,H,hpg,lens,cuts", [
+    (8, 12, 6, 2, [23, 4], ([7, 1], [1, 1], [15, 2])), (5, 33, 2, 1, [23, 4], ([7, 1], [1, 1], [15, 2])),
+    (48, 64, 4, 4, [23, 4], ([7, 1], [1, 1], [15, 2])), (130, 8, 1, 1, [23, 4], ([7, 1], [1, 1], [15, 2])),
+    (20, 36, 2, 2, [521, 270], ([200, 3], [1, 1], [320, 266]))])
+def test_linear_scan_kernel(mode, N, P_, H, hpg, lens, cuts):
     """The recurrence alone against a loop over tokens, cut into steps of several sizes (one token included), with
-    key sizes that are no multiple of four and value sizes that are no multiple of the tile."""
+    key sizes that are no multiple of four and value sizes that are no multiple of the tile; the long case runs in
+    segments side by side (a sequence of one segment beside one of several, a last segment that is short)."""
     from picolm_b200 import ops
     if mode == "sigmoid":
         hpg = 1
     dev = "cuda:0"
     g = torch.Generator().manual_seed(N * 7 + P_)
     G = H // hpg
-    lens = [23, 4]
     q = [torch.randn(n, G * N, generator=g) for n in lens]
     k = [torch.randn(n, G * N, generator=g) for n in lens]
     v = [torch.randn(n, H * P_, generator=g) for n in lens]
@@ -178,7 +181,7 @@ def test_linear_scan_kernel(mode, N, P_, H, hpg):
     state = torch.zeros(4, H * N * P_, device=dev)
     slots = [2, 0]
     got, at = [[], []], [0, 0]
-    for cut in ([7, 1], [1, 1], [15, 2]):
+    for cut in cuts:
         step = _Step(cut, slots, dev)
         cat = lambda xs: torch.cat([xs[i][at[i]:at[i] + n] for i, n in enumerate(cut)]).to(dev)   # noqa: E731
         y = ops.linear_scan(cat(q), cat(k), cat(v), cat(raw), ops.DECAY_STEP if mode == "step" else ops.DECAY_SIGMOID,
@@ -225,6 +228,48 @@ def test_gated_norm_and_head_linear_kernels():
     assert torch.allclose(ops.head_linear(xs[:, 2:], W).double().cpu(), want, atol=1e-4, rtol=1e-5)
     assert torch.allclose(ops.head_linear(xs[:, 2:], W, gate=gt).double().cpu(), want * torch.sigmoid(gt.double().cpu()),
                           atol=1e-4, rtol=1e-5)
+
+
+def test_closing_norm_add_and_opening_norm_in_one_kernel():
+    from picolm_b200 import ops
+    dev = "cuda:0"
+    g = torch.Generator().manual_seed(11)
+    for T, d, wt in ((5, 40, torch.float32), (3, 2048, torch.bfloat16), (2, 5000, torch.float32)):
+        x, delta = torch.randn(T, d, generator=g).to(dev), (3 * torch.randn(T, d, generator=g)).to(dev)
+        w1, w2 = torch.randn(d, generator=g).to(wt).to(dev), torch.randn(d, generator=g).to(wt).to(dev)
+        new_x = x.double().cpu() + P.rms_norm(delta.double().cpu(), w1.double().cpu(), 1e-5)
+        want = P.rms_norm(new_x, w2.double().cpu(), 1e-6)
+        got = ops.post_pre_norm(x, delta, w1, 1e-5, w2, 1e-6, torch.float32)
+        assert torch.allclose(x.double().cpu(), new_x, atol=1e-5, rtol=1e-5)
+        assert torch.allclose(got.double().cpu(), want, atol=1e-5, rtol=1e-5)
+    # the same bits as the two kernels it stands for
+    x, delta = torch.randn(4, 64, generator=g).to(dev), torch.randn(4, 64, generator=g).to(dev)
+    w1, w2 = torch.randn(64, generator=g).to(dev), torch.randn(64, generator=g).to(dev)
+    xa, xb = x.clone(), x.clone()
+    one = ops.post_pre_norm(xa, delta, w1, 1e-5, w2, 1e-5, torch.float32)
+    two = ops.rmsnorm(xb, w2, 1e-5, torch.float32, delta=ops.rmsnorm(delta.clone(), w1, 1e-5, torch.float32))
+    assert torch.equal(xa, xb) and torch.equal(one, two)
+
+
+def test_gated_product_with_the_tanh_form_of_gelu():
+    """The feed-forward's first product with GELU in its epilogue (a build variant of the tensor-core kernels), for
+    a decode-shaped and a prompt-shaped step, against the activation worked out from the rounded products."""
+    from picolm_b200 import ops
+    dev = "cuda:0"
+    g = torch.Generator().manual_seed(12)
+    K, F = 256, 384
+    gate = (torch.randn(F, K, generator=g) / 8).to(torch.bfloat16).to(dev)
+    up = (torch.randn(F, K, generator=g) / 8).to(torch.bfloat16).to(dev)
+    w = ops.interleave_gate_up(gate, up)
+    for T in (7, 300):
+        h = torch.randn(T, K, generator=g).to(torch.bfloat16).to(dev)
+        gg = (h.double().cpu() @ gate.double().cpu().T).to(torch.bfloat16).double()
+        uu = (h.double().cpu() @ up.double().cpu().T).to(torch.bfloat16).double()
+        want = P.gelu_tanh(gg) * uu
+        got = ops.linear_swiglu(h, w, activation="gelu_tanh").double().cpu()
+        assert (got - want).abs().max() <= 0.02 * want.abs().max(), T
+        silu = ops.linear_swiglu(h, w).double().cpu()
+        assert (silu - P.silu(gg) * uu).abs().max() <= 0.02 * want.abs().max(), "the plain build still applies SiLU"
 
 
 # ------------------------------------------------------------------------------------ each mixer as a model
