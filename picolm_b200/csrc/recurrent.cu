@@ -22,9 +22,33 @@ __device__ __forceinline__ float log_sigmoid_f(float x) { return fminf(x, 0.f) -
 __device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); }
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + expf(-x)); }
 
+// Two fp32 lanes in a 64-bit register; fma.rn.f32x2 rounds each lane as the scalar fma does.
+__device__ __forceinline__ uint64_t pack2f(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(__float_as_uint(lo)), "r"(__float_as_uint(hi)));
+    return r;
+}
+__device__ __forceinline__ void load8_bf16(const bf16* p, float* f) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        f[2 * e] = __low2float(h2[e]);
+        f[2 * e + 1] = __high2float(h2[e]);
+    }
+}
+__device__ __forceinline__ float lo2f(uint64_t v) { return __uint_as_float((uint32_t)v); }
+__device__ __forceinline__ float hi2f(uint64_t v) { return __uint_as_float((uint32_t)(v >> 32)); }
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+
 // ------------------------------------------------------------------------------------------------ convolution
-// u [T, C] with row stride ldu; w [C, taps], the last tap being the current token's; state [slot][taps - 1][C],
-// oldest first.  One thread per (token, channel): inputs before the step's first token come from the state.
+// u [T, C] with row stride ldu; w [taps, C] (tap-major, so that neighbouring channels' weights are neighbours), the
+// last tap being the current token's; state [slot][taps - 1][C], oldest first.  One block row per token, one thread
+// per channel: inputs before the step's first token come from the state.
 template <typename T>
 __global__ void causal_conv_kernel(const T* __restrict__ u, long ldu, const float* __restrict__ w, const float* __restrict__ bias,
                                    const float* __restrict__ state, long state_stride, const int* __restrict__ tok_seq,
@@ -32,9 +56,8 @@ __global__ void causal_conv_kernel(const T* __restrict__ u, long ldu, const floa
                                    int n_tokens, int C, int taps) {
     pdl_launch_dependents();
     pdl_wait();
-    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= (long)n_tokens * C) return;
-    const int t = (int)(idx / C), c = (int)(idx % C);
+    const int t = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= C) return;
     const int b = PLM_SEQ_NO(tok_seq[t]);
     const int i = t - seq_start[b];
     const float* st = state + (long)seq_slot[b] * state_stride;
@@ -42,9 +65,52 @@ __global__ void causal_conv_kernel(const T* __restrict__ u, long ldu, const floa
     for (int j = 0; j < taps; ++j) {
         const int back = taps - 1 - j, li = i - back;
         const float val = li >= 0 ? to_f32<T>(u[(long)(t - back) * ldu + c]) : st[(long)(taps - 1 + li) * C + c];
-        acc = fmaf(w[(long)c * taps + j], val, acc);
+        acc = fmaf(w[(long)j * C + c], val, acc);
     }
     out[(long)t * C + c] = from_f32<T>(silu_f(acc));
+}
+
+// The same for bf16 rows whose channels come in eights on 16-byte boundaries: a thread takes 8 channels of a token
+// with one 16-byte load per tap.
+__global__ void causal_conv_vec8_kernel(const bf16* __restrict__ u, long ldu, const float* __restrict__ w,
+                                        const float* __restrict__ bias, const float* __restrict__ state, long state_stride,
+                                        const int* __restrict__ tok_seq, const int* __restrict__ seq_start,
+                                        const int* __restrict__ seq_slot, bf16* __restrict__ out, int n_tokens, int C, int taps) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x, c = (blockIdx.y * blockDim.x + threadIdx.x) << 3;
+    if (c >= C) return;
+    const int b = PLM_SEQ_NO(tok_seq[t]);
+    const int i = t - seq_start[b];
+    const float* st = state + (long)seq_slot[b] * state_stride;
+    float acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = bias ? bias[c + e] : 0.f;
+    for (int j = 0; j < taps; ++j) {
+        const int back = taps - 1 - j, li = i - back;
+        float val[8];
+        if (li >= 0) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(u + (long)(t - back) * ldu + c);
+            const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                val[2 * e] = __low2float(h2[e]);
+                val[2 * e + 1] = __high2float(h2[e]);
+            }
+        } else {
+            const float* sr = st + (long)(taps - 1 + li) * C + c;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) val[e] = sr[e];
+        }
+        const float4 w0 = *reinterpret_cast<const float4*>(w + (long)j * C + c), w1 = *reinterpret_cast<const float4*>(w + (long)j * C + c + 4);
+        const float wr[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] = fmaf(wr[e], val[e], acc[e]);
+    }
+    __nv_bfloat162 o[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[e] = __floats2bfloat162_rn(silu_f(acc[2 * e]), silu_f(acc[2 * e + 1]));
+    *reinterpret_cast<uint4*>(out + (long)t * C + c) = *reinterpret_cast<const uint4*>(o);
 }
 
 // The state after the step: the last taps - 1 inputs of old state followed by the step's tokens.  One thread per
@@ -82,10 +148,10 @@ __global__ void causal_conv_decode_kernel(const T* __restrict__ u, long ldu, con
     float acc = bias ? bias[c] : 0.f;
     for (int j = 0; j < taps - 1; ++j) {
         const float val = st[(long)j * C + c];
-        acc = fmaf(w[(long)c * taps + j], val, acc);
+        acc = fmaf(w[(long)j * C + c], val, acc);
         if (j > 0) st[(long)(j - 1) * C + c] = val;
     }
-    acc = fmaf(w[(long)c * taps + taps - 1], cur, acc);
+    acc = fmaf(w[(long)(taps - 1) * C + c], cur, acc);
     if (taps > 1) st[(long)(taps - 2) * C + c] = cur;
     out[(long)b * C + c] = from_f32<T>(silu_f(acc));
 }
@@ -106,11 +172,16 @@ extern "C" int plm_causal_conv(const void* u, int dtype, long ldu, const float* 
                              state_stride, seq_slot, (bf16*)out, n_seqs, C, taps);
         return plm_status_of(e);
     }
-    const unsigned grid = (unsigned)(((long)n_tokens * C + nt - 1) / nt);
+    const dim3 grid((unsigned)n_tokens, (unsigned)((C + nt - 1) / nt));
+    if (dtype == PLM_BF16 && C % 8 == 0 && ldu % 8 == 0 && (uintptr_t)u % 16 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)w % 16 == 0)
+        e = launch_pdl(causal_conv_vec8_kernel, dim3((unsigned)n_tokens, (unsigned)((C / 8 + 127) / 128)), dim3(128), 0, stream,
+                       (const bf16*)u, ldu, w, bias, (const float*)state, state_stride, tok_seq, seq_start, seq_slot, (bf16*)out,
+                       n_tokens, C, taps);
+    else
     e = dtype == PLM_F32
-            ? launch_pdl(causal_conv_kernel<float>, dim3(grid), dim3(nt), 0, stream, (const float*)u, ldu, w, bias, (const float*)state,
+            ? launch_pdl(causal_conv_kernel<float>, grid, dim3(nt), 0, stream, (const float*)u, ldu, w, bias, (const float*)state,
                          state_stride, tok_seq, seq_start, seq_slot, (float*)out, n_tokens, C, taps)
-            : launch_pdl(causal_conv_kernel<bf16>, dim3(grid), dim3(nt), 0, stream, (const bf16*)u, ldu, w, bias, (const float*)state,
+            : launch_pdl(causal_conv_kernel<bf16>, grid, dim3(nt), 0, stream, (const bf16*)u, ldu, w, bias, (const float*)state,
                          state_stride, tok_seq, seq_start, seq_slot, (bf16*)out, n_tokens, C, taps);
     if (e != cudaSuccess) return (int)e;
     if (taps == 1) return PLM_OK;
@@ -127,8 +198,11 @@ extern "C" int plm_causal_conv(const void* u, int dtype, long ldu, const float* 
 // How the decay d_t and the scale of v_t come out of the raw projections (all in fp32):
 //   DECAY_STEP     per head: dt = softplus(raw[t, h] + p0[h]); d = exp(-exp(p1[h]) * dt); v_t is scaled by dt
 //   DECAY_SIGMOID  per key channel: d[n] = exp(log_sigmoid(raw[t, h * N + n] + p0[h * N + n]) * power)
+//   DECAY_GIVEN    per key channel, worked out beforehand: d[n] = raw[t, h * N + n], float32 (plm_sigmoid_decay
+//                  makes these from the raw values where a step's tokens are walked twice)
 #define DECAY_STEP 1
 #define DECAY_SIGMOID 2
+#define DECAY_GIVEN 3
 
 // What a launch of the scan kernel does with the tokens of its segment:
 //   SCAN_WHOLE  one segment per sequence: from the cache's state, writes y and the state (decode steps, short prompts)
@@ -152,6 +226,7 @@ struct ScanArgs {
     int n_seqs, H, N, P, heads_per_group;
     int seg_len, max_segs;                // tokens per segment; segments of the longest sequence
     float *seg_state, *seg_decay;         // [seq][segment][H][N][P] and [seq][segment][H][N]
+    int vec8;                             // bf16 rows may be read eight channels at a time (sizes and addresses allow it)
 };
 
 // One block per (sequence, head, tile of 32 value columns, segment).  A warp holds 8 columns, two groups of 4; the
@@ -160,9 +235,9 @@ struct ScanArgs {
 // k, decay and v to shared memory as fp32 (the exponentials are taken there, once per token and channel), then every
 // thread steps its piece of the state through them; y's sum over the rows goes through the 16 lanes by shuffles.
 template <typename T, int NS, int MODE, int PASS>
-__global__ void __launch_bounds__(SCAN_THREADS) linear_scan_kernel(const ScanArgs a, int TC) {
+__global__ void __launch_bounds__(SCAN_THREADS, NS <= 8 ? 4 : 1) linear_scan_kernel(const ScanArgs a, int TC) {
     constexpr int ROW = NS == 4 ? 4 : NS + 4;             // padded so that a quarter warp's float4 reads hit different banks
-    constexpr bool PER_CHANNEL = MODE == DECAY_SIGMOID;
+    constexpr bool PER_CHANNEL = MODE != DECAY_STEP;
     extern __shared__ __align__(16) float smem[];
     pdl_launch_dependents();
     const int ptiles = (a.P + SCAN_PTILE - 1) / SCAN_PTILE;
@@ -195,30 +270,78 @@ __global__ void __launch_bounds__(SCAN_THREADS) linear_scan_kernel(const ScanArg
     float* st = a.state + (long)a.seq_slot[b] * a.state_stride + (long)h * N * P;
     float* sg = PASS == SCAN_WHOLE ? nullptr : a.seg_state + (((long)b * a.max_segs + seg) * a.H + h) * N * P;
     const float* init = PASS == SCAN_WHOLE ? st : PASS == SCAN_FINAL ? sg : nullptr;
-    float S[NS][4];
-    float dprod[PER_CHANNEL ? NS : 1];
+    // The state in pairs of rows (2i, 2i + 1) of one column: the rows' k, q and decay lie side by side in shared
+    // memory, so fma.rn.f32x2 takes them as they come and every instruction steps two elements of the state.
+    uint64_t S[NS / 2][4];
+    uint64_t dprod[PER_CHANNEL ? NS / 2 : 1];
+    float dprod_h = 1.f;
 #pragma unroll
-    for (int i = 0; i < (PER_CHANNEL ? NS : 1); ++i) dprod[i] = 1.f;
+    for (int i = 0; i < (PER_CHANNEL ? NS / 2 : 1); ++i) dprod[i] = pack2f(1.f, 1.f);
 #pragma unroll
-    for (int i = 0; i < NS; ++i) {
-        const int n = npart * NS + i;
+    for (int i = 0; i < NS / 2; ++i) {
+        const int n = npart * NS + 2 * i;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) S[i][j] = (init && n < N && p + j < P) ? init[(long)n * P + p + j] : 0.f;
+        for (int j = 0; j < 4; ++j)
+            S[i][j] = pack2f((init && n < N && p + j < P) ? init[(long)n * P + p + j] : 0.f,
+                             (init && n + 1 < N && p + j < P) ? init[(long)(n + 1) * P + p + j] : 0.f);
     }
     const float skip = a.skip ? a.skip[h] : 0.f;
+    // Rows of bf16 whose channels come in eights on 16-byte boundaries are brought in eight at a time (a.vec8, checked
+    // by the host); the channels beyond N, which only pad the 16 lanes' shares, are filled once.
+    const bool vec8 = sizeof(T) == 2 && a.vec8;
+    if (vec8) {
+        for (int idx = threadIdx.x; idx < TC * 16 * NS; idx += SCAN_THREADS) {
+            const int tt = idx / (16 * NS), n = idx % (16 * NS);
+            if (n < N) continue;
+            const int at = (tt * 16 + n / NS) * ROW + n % NS;
+            qs[at] = 0.f, ks[at] = 0.f;
+            if (PER_CHANNEL) ds[at] = 1.f;
+        }
+    }
     for (int base = t0; base < t1; base += TC) {
         const int nt = min(TC, t1 - base);
         __syncthreads();
+        if (vec8) {
+            const int groups = N >> 3;
 #pragma unroll 2
-        for (int idx = threadIdx.x; idx < nt * 16 * NS; idx += SCAN_THREADS) {
-            const int tt = idx / (16 * NS), n = idx % (16 * NS);
-            const int at = (tt * 16 + n / NS) * ROW + n % NS;
-            const long row = base + tt;
-            const bool in = n < N;
-            if (PASS != SCAN_LOCAL) qs[at] = in ? to_f32<T>(q[row * a.ldq + (long)g * N + n]) * a.q_scale : 0.f;
-            ks[at] = in ? to_f32<T>(k[row * a.ldk + (long)g * N + n]) : 0.f;
-            if (PER_CHANNEL)
-                ds[at] = in ? expf(log_sigmoid_f(to_f32<T>(raw[row * a.ldraw + (long)h * N + n]) + a.p0[(long)h * N + n]) * a.power) : 1.f;
+            for (int idx = threadIdx.x; idx < nt * groups; idx += SCAN_THREADS) {
+                const int tt = idx / groups, n = (idx % groups) << 3;
+                const int at = (tt * 16 + n / NS) * ROW + n % NS;
+                const long row = base + tt;
+                float f[8];
+                if (PASS != SCAN_LOCAL) {
+                    load8_bf16((const bf16*)q + row * a.ldq + (long)g * N + n, f);
+                    *(float4*)(qs + at) = make_float4(f[0] * a.q_scale, f[1] * a.q_scale, f[2] * a.q_scale, f[3] * a.q_scale);
+                    *(float4*)(qs + at + 4) = make_float4(f[4] * a.q_scale, f[5] * a.q_scale, f[6] * a.q_scale, f[7] * a.q_scale);
+                }
+                load8_bf16((const bf16*)k + row * a.ldk + (long)g * N + n, f);
+                *(float4*)(ks + at) = make_float4(f[0], f[1], f[2], f[3]);
+                *(float4*)(ks + at + 4) = make_float4(f[4], f[5], f[6], f[7]);
+                if (MODE == DECAY_GIVEN) {
+                    const float* dr = (const float*)a.raw + row * a.ldraw + (long)h * N + n;
+                    *(float4*)(ds + at) = *(const float4*)dr;
+                    *(float4*)(ds + at + 4) = *(const float4*)(dr + 4);
+                }
+                if (MODE == DECAY_SIGMOID) {
+                    load8_bf16((const bf16*)raw + row * a.ldraw + (long)h * N + n, f);
+                    const float* bias = a.p0 + (long)h * N + n;
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) ds[at + e] = expf(log_sigmoid_f(f[e] + bias[e]) * a.power);
+                }
+            }
+        } else {
+#pragma unroll 8
+            for (int idx = threadIdx.x; idx < nt * 16 * NS; idx += SCAN_THREADS) {
+                const int tt = idx / (16 * NS), n = idx % (16 * NS);
+                const int at = (tt * 16 + n / NS) * ROW + n % NS;
+                const long row = base + tt;
+                const bool in = n < N;
+                if (PASS != SCAN_LOCAL) qs[at] = in ? to_f32<T>(q[row * a.ldq + (long)g * N + n]) * a.q_scale : 0.f;
+                ks[at] = in ? to_f32<T>(k[row * a.ldk + (long)g * N + n]) : 0.f;
+                if (MODE == DECAY_SIGMOID)
+                    ds[at] = in ? expf(log_sigmoid_f(to_f32<T>(raw[row * a.ldraw + (long)h * N + n]) + a.p0[(long)h * N + n]) * a.power) : 1.f;
+                if (MODE == DECAY_GIVEN) ds[at] = in ? ((const float*)a.raw)[row * a.ldraw + (long)h * N + n] : 1.f;
+            }
         }
         if (!PER_CHANNEL) {
             for (int tt = threadIdx.x; tt < nt; tt += SCAN_THREADS) {
@@ -227,9 +350,20 @@ __global__ void __launch_bounds__(SCAN_THREADS) linear_scan_kernel(const ScanArg
                 ds[TC + tt] = dt;
             }
         }
-        for (int idx = threadIdx.x; idx < nt * SCAN_PTILE; idx += SCAN_THREADS) {
-            const int tt = idx / SCAN_PTILE, c = idx % SCAN_PTILE, pc = ptile * SCAN_PTILE + c;
-            vs[idx] = pc < P ? to_f32<T>(v[(long)(base + tt) * a.ldv + (long)h * P + pc]) : 0.f;
+        if (vec8 && ptile * SCAN_PTILE + SCAN_PTILE <= P) {
+            for (int idx = threadIdx.x; idx < nt * (SCAN_PTILE / 8); idx += SCAN_THREADS) {
+                const int tt = idx / (SCAN_PTILE / 8), c = (idx % (SCAN_PTILE / 8)) << 3;
+                float f[8];
+                load8_bf16((const bf16*)v + (long)(base + tt) * a.ldv + (long)h * P + ptile * SCAN_PTILE + c, f);
+                *(float4*)(vs + tt * SCAN_PTILE + c) = make_float4(f[0], f[1], f[2], f[3]);
+                *(float4*)(vs + tt * SCAN_PTILE + c + 4) = make_float4(f[4], f[5], f[6], f[7]);
+            }
+        } else {
+#pragma unroll 4
+            for (int idx = threadIdx.x; idx < nt * SCAN_PTILE; idx += SCAN_THREADS) {
+                const int tt = idx / SCAN_PTILE, c = idx % SCAN_PTILE, pc = ptile * SCAN_PTILE + c;
+                vs[idx] = pc < P ? to_f32<T>(v[(long)(base + tt) * a.ldv + (long)h * P + pc]) : 0.f;
+            }
         }
         __syncthreads();
         for (int tt = 0; tt < nt; ++tt) {
@@ -237,48 +371,51 @@ __global__ void __launch_bounds__(SCAN_THREADS) linear_scan_kernel(const ScanArg
             const float vsc = PER_CHANNEL ? 1.f : ds[TC + tt];
             const float4 vv = make_float4(vsc * x.x, vsc * x.y, vsc * x.z, vsc * x.w);
             const float dh = PER_CHANNEL ? 0.f : ds[tt];
-            if (!PER_CHANNEL) dprod[0] *= dh;
-            const float4* q4 = (const float4*)(qs + (tt * 16 + npart) * ROW);
-            const float4* k4 = (const float4*)(ks + (tt * 16 + npart) * ROW);
-            const float4* d4 = (const float4*)(ds + (tt * 16 + npart) * ROW);
-            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (!PER_CHANNEL && PASS == SCAN_LOCAL) dprod_h *= dh;
+            const uint64_t dh2 = pack2f(dh, dh), zero2 = 0ull;
+            const uint64_t vv2[4] = {pack2f(vv.x, vv.x), pack2f(vv.y, vv.y), pack2f(vv.z, vv.z), pack2f(vv.w, vv.w)};
+            const ulonglong2* q2 = (const ulonglong2*)(qs + (tt * 16 + npart) * ROW);
+            const ulonglong2* k2 = (const ulonglong2*)(ks + (tt * 16 + npart) * ROW);
+            const ulonglong2* d2 = (const ulonglong2*)(ds + (tt * 16 + npart) * ROW);
+            uint64_t acc2[4] = {zero2, zero2, zero2, zero2};
 #pragma unroll
             for (int i4 = 0; i4 < NS / 4; ++i4) {
-                const float4 kk = k4[i4];
-                float4 qq = make_float4(0.f, 0.f, 0.f, 0.f), dd = make_float4(dh, dh, dh, dh);
-                if (PASS != SCAN_LOCAL) qq = q4[i4];
-                if (PER_CHANNEL) dd = d4[i4];
-                const float kr[4] = {kk.x, kk.y, kk.z, kk.w}, qr[4] = {qq.x, qq.y, qq.z, qq.w}, dr[4] = {dd.x, dd.y, dd.z, dd.w};
+                const ulonglong2 kk = k2[i4];
+                ulonglong2 qq = make_ulonglong2(zero2, zero2), dd = make_ulonglong2(dh2, dh2);
+                if (PASS != SCAN_LOCAL) qq = q2[i4];
+                if (PER_CHANNEL) dd = d2[i4];
 #pragma unroll
-                for (int r = 0; r < 4; ++r) {
-                    float* Sr = S[4 * i4 + r];
-                    if (PER_CHANNEL) dprod[4 * i4 + r] *= dr[r];
-                    Sr[0] = fmaf(dr[r], Sr[0], kr[r] * vv.x);
-                    Sr[1] = fmaf(dr[r], Sr[1], kr[r] * vv.y);
-                    Sr[2] = fmaf(dr[r], Sr[2], kr[r] * vv.z);
-                    Sr[3] = fmaf(dr[r], Sr[3], kr[r] * vv.w);
-                    if (PASS != SCAN_LOCAL) {
-                        acc.x = fmaf(Sr[0], qr[r], acc.x);
-                        acc.y = fmaf(Sr[1], qr[r], acc.y);
-                        acc.z = fmaf(Sr[2], qr[r], acc.z);
-                        acc.w = fmaf(Sr[3], qr[r], acc.w);
+                for (int half = 0; half < 2; ++half) {
+                    const uint64_t kp = half ? kk.y : kk.x, qp = half ? qq.y : qq.x, dp = half ? dd.y : dd.x;
+                    uint64_t* Sr = S[2 * i4 + half];
+                    if (PER_CHANNEL && PASS == SCAN_LOCAL) dprod[2 * i4 + half] = fma2(dprod[2 * i4 + half], dp, zero2);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        Sr[j] = fma2(dp, Sr[j], fma2(kp, vv2[j], zero2));
+                        if (PASS != SCAN_LOCAL) acc2[j] = fma2(Sr[j], qp, acc2[j]);
                     }
                 }
             }
+            float4 acc;
+            acc.x = lo2f(acc2[0]) + hi2f(acc2[0]);
+            acc.y = lo2f(acc2[1]) + hi2f(acc2[1]);
+            acc.z = lo2f(acc2[2]) + hi2f(acc2[2]);
+            acc.w = lo2f(acc2[3]) + hi2f(acc2[3]);
             if (PASS != SCAN_LOCAL) {
-#pragma unroll
-                for (int o = 1; o < 16; o <<= 1) {
-                    acc.x += __shfl_xor_sync(0xffffffffu, acc.x, o);
-                    acc.y += __shfl_xor_sync(0xffffffffu, acc.y, o);
-                    acc.z += __shfl_xor_sync(0xffffffffu, acc.z, o);
-                    acc.w += __shfl_xor_sync(0xffffffffu, acc.w, o);
-                }
-                if (npart == 0) {
-                    float* yr = a.y + (long)(base + tt) * a.ldy + (long)h * P + p;
-                    const float out[4] = {fmaf(skip, x.x, acc.x), fmaf(skip, x.y, acc.y), fmaf(skip, x.z, acc.z), fmaf(skip, x.w, acc.w)};
-#pragma unroll
-                    for (int j = 0; j < 4; ++j)
-                        if (p + j < P) yr[j] = out[j];
+                // Four sums over the 16 lanes in five shuffles: a lane gives away the half of its values that its
+                // partner keeps (columns 0, 1 stay where bit 3 of the lane is clear, then one of the two where bit 2
+                // is), after which lanes 0, 4, 8 and 12 of the group end up with the totals of columns 0, 1, 2, 3.
+                const bool hi8 = npart & 8, hi4 = npart & 4;
+                const float k0 = hi8 ? acc.z : acc.x, k1 = hi8 ? acc.w : acc.y;
+                const float g0 = hi8 ? acc.x : acc.z, g1 = hi8 ? acc.y : acc.w;
+                const float r0 = k0 + __shfl_xor_sync(0xffffffffu, g0, 8), r1 = k1 + __shfl_xor_sync(0xffffffffu, g1, 8);
+                float tot = (hi4 ? r1 : r0) + __shfl_xor_sync(0xffffffffu, hi4 ? r0 : r1, 4);
+                tot += __shfl_xor_sync(0xffffffffu, tot, 2);
+                tot += __shfl_xor_sync(0xffffffffu, tot, 1);
+                if ((npart & 3) == 0) {
+                    const int j = npart >> 2;                 // which of the thread group's four columns this lane holds
+                    const float xj = j == 0 ? x.x : j == 1 ? x.y : j == 2 ? x.z : x.w;
+                    if (p + j < P) a.y[(long)(base + tt) * a.ldy + (long)h * P + p + j] = fmaf(skip, xj, tot);
                 }
             }
         }
@@ -286,11 +423,13 @@ __global__ void __launch_bounds__(SCAN_THREADS) linear_scan_kernel(const ScanArg
     float* dst = PASS == SCAN_LOCAL ? sg : (PASS == SCAN_WHOLE || seg == n_segs - 1) ? st : nullptr;
     if (dst) {
 #pragma unroll
-        for (int i = 0; i < NS; ++i) {
-            const int n = npart * NS + i;
+        for (int i = 0; i < NS / 2; ++i) {
+            const int n = npart * NS + 2 * i;
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
-                if (n < N && p + j < P) dst[(long)n * P + p + j] = S[i][j];
+            for (int j = 0; j < 4; ++j) {
+                if (n < N && p + j < P) dst[(long)n * P + p + j] = lo2f(S[i][j]);
+                if (n + 1 < N && p + j < P) dst[(long)(n + 1) * P + p + j] = hi2f(S[i][j]);
+            }
         }
     }
     if (PASS == SCAN_LOCAL && ptile == 0 && warp == 0 && pg == 0) {
@@ -298,7 +437,8 @@ __global__ void __launch_bounds__(SCAN_THREADS) linear_scan_kernel(const ScanArg
 #pragma unroll
         for (int i = 0; i < NS; ++i) {
             const int n = npart * NS + i;
-            if (n < N) dd[n] = PER_CHANNEL ? dprod[PER_CHANNEL ? i : 0] : dprod[0];
+            const uint64_t pr = dprod[PER_CHANNEL ? i / 2 : 0];
+            if (n < N) dd[n] = PER_CHANNEL ? ((i & 1) ? hi2f(pr) : lo2f(pr)) : dprod_h;
         }
     }
 }
@@ -319,10 +459,22 @@ __global__ void scan_combine_kernel(const ScanArgs a) {
     float S = a.state[(long)a.seq_slot[b] * a.state_stride + e];
     float* sg = a.seg_state + (long)b * a.max_segs * per_seq + e;
     const float* dd = a.seg_decay + (long)b * a.max_segs * a.H * a.N + hn;
-    for (int c = 0; c < n_segs; ++c) {
-        const float local = c < n_segs - 1 ? sg[(long)c * per_seq] : 0.f;
-        sg[(long)c * per_seq] = S;
-        if (c < n_segs - 1) S = fmaf(dd[(long)c * a.H * a.N], S, local);
+    // eight segments' values are asked for at once, then chained
+    for (int c0 = 0; c0 < n_segs; c0 += 8) {
+        float local[8], decay[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int c = c0 + i;
+            const bool more = c < n_segs - 1;
+            local[i] = more ? sg[(long)c * per_seq] : 0.f;
+            decay[i] = more ? dd[(long)c * a.H * a.N] : 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int c = c0 + i;
+            if (c < n_segs) sg[(long)c * per_seq] = S;
+            if (c < n_segs - 1) S = fmaf(decay[i], S, local[i]);
+        }
     }
 }
 
@@ -330,7 +482,7 @@ template <int NS>
 static size_t scan_smem(int mode, int* TC) {
     const int ROW = NS == 4 ? 4 : NS + 4;
     // tokens per pass: as many as fit into about 40 KB of shared memory, 16 at most
-    const long per_token = (mode == DECAY_SIGMOID ? 3L : 2L) * 16 * ROW + SCAN_PTILE + (mode == DECAY_SIGMOID ? 0 : 2);
+    const long per_token = (mode != DECAY_STEP ? 3L : 2L) * 16 * ROW + SCAN_PTILE + (mode != DECAY_STEP ? 0 : 2);
     int tc = (int)((40 * 1024 / 4 - 4) / per_token);
     tc = tc > 16 ? 16 : tc < 1 ? 1 : tc;
     *TC = tc;
@@ -358,7 +510,10 @@ template <typename T>
 static int scan_dispatch(const ScanArgs& a, int mode, cudaStream_t stream) {
     const int ns = (a.N + 15) / 16;
     cudaError_t e;
-#define SCAN_NS(NS_) (mode == DECAY_SIGMOID ? scan_launch<T, NS_, DECAY_SIGMOID>(a, stream) : scan_launch<T, NS_, DECAY_STEP>(a, stream))
+#define SCAN_NS(NS_)                                                                       \
+    (mode == DECAY_SIGMOID ? scan_launch<T, NS_, DECAY_SIGMOID>(a, stream)                 \
+     : mode == DECAY_GIVEN ? scan_launch<T, NS_, DECAY_GIVEN>(a, stream)                   \
+                           : scan_launch<T, NS_, DECAY_STEP>(a, stream))
     if (ns <= 4) e = SCAN_NS(4);
     else if (ns <= 8) e = SCAN_NS(8);
     else if (ns <= 16) e = SCAN_NS(16);
@@ -369,15 +524,16 @@ static int scan_dispatch(const ScanArgs& a, int mode, cudaStream_t stream) {
 
 // How a step whose longest sequence brings `max_new` tokens is cut: out[0] tokens per segment, out[1] segments of the
 // longest sequence (1: one pass from the cache's state, no scratch memory).  Segments are worth their second pass
-// when the sequences alone leave most of the GPU idle; there are as many as give every SM a few blocks, each of at
-// least 64 tokens, and no more than keep the scratch memory under 1 GiB.
+// when the sequences alone leave most of the GPU idle; there are as many as make one wave of blocks (a second, partly
+// filled wave would take as long as the first), each of at least 64 tokens, and no more than keep the scratch memory
+// under 1 GiB.
 extern "C" int plm_linear_scan_plan(int n_seqs, int H, int N, int P, int max_new, int* out) {
     out[0] = max_new > 0 ? max_new : 1;
     out[1] = 1;
     if (n_seqs <= 0 || H <= 0 || N <= 0 || P <= 0) return PLM_ERR_SHAPE;
     if (max_new < 192) return PLM_OK;
     const long blocks = (long)n_seqs * H * ((P + SCAN_PTILE - 1) / SCAN_PTILE);
-    long segs = (6L * PLM_SM_COUNT + blocks - 1) / blocks;
+    long segs = 4L * PLM_SM_COUNT / blocks;               // four blocks an SM run at once: one wave of them
     const long most = max_new / 64;
     if (segs > most) segs = most;
     const long state_bytes = (long)n_seqs * H * N * (P + 1) * 4;
@@ -390,6 +546,32 @@ extern "C" int plm_linear_scan_plan(int n_seqs, int H, int N, int P, int max_new
     return PLM_OK;
 }
 
+// out[t, c] = sigmoid(raw[t, c] + bias[c]) ^ power in fp32: the decays of DECAY_SIGMOID, worked out once.
+template <typename T>
+__global__ void sigmoid_decay_kernel(const T* __restrict__ raw, long ld, const float* __restrict__ bias, float power,
+                                     float* __restrict__ out, int n_rows, int C) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long)n_rows * C) return;
+    const long t = idx / C;
+    const int c = (int)(idx % C);
+    out[idx] = expf(log_sigmoid_f(to_f32<T>(raw[t * ld + c]) + bias[c]) * power);
+}
+
+extern "C" int plm_sigmoid_decay(const void* raw, int dtype, long ld, const float* bias, float power, float* out, int n_rows,
+                                 int C, cudaStream_t stream) {
+    if (n_rows <= 0 || C <= 0) return PLM_ERR_SHAPE;
+    const unsigned grid = (unsigned)(((long)n_rows * C + 255) / 256);
+    if (dtype == PLM_F32)
+        return plm_status_of(launch_pdl(sigmoid_decay_kernel<float>, dim3(grid), dim3(256), 0, stream, (const float*)raw, ld, bias,
+                                        power, out, n_rows, C));
+    if (dtype == PLM_BF16)
+        return plm_status_of(launch_pdl(sigmoid_decay_kernel<bf16>, dim3(grid), dim3(256), 0, stream, (const bf16*)raw, ld, bias,
+                                        power, out, n_rows, C));
+    return PLM_ERR_DTYPE;
+}
+
 extern "C" int plm_linear_scan(const void* q, const void* k, const void* v, const void* raw, int dtype, long ldq, long ldk,
                                long ldv, long ldraw, int mode, const float* p0, const float* p1, const float* skip,
                                float q_scale, float power, float* state, long state_stride, float* y, long ldy,
@@ -397,9 +579,9 @@ extern "C" int plm_linear_scan(const void* q, const void* k, const void* v, cons
                                int heads_per_group, int seg_len, int max_segs, float* seg_state, float* seg_decay,
                                cudaStream_t stream) {
     if (n_seqs <= 0 || H <= 0 || N <= 0 || P <= 0 || heads_per_group <= 0) return PLM_ERR_SHAPE;
-    if (mode != DECAY_STEP && mode != DECAY_SIGMOID) return PLM_ERR_UNSUPPORTED;
+    if (mode != DECAY_STEP && mode != DECAY_SIGMOID && mode != DECAY_GIVEN) return PLM_ERR_UNSUPPORTED;
     if (mode == DECAY_STEP && !p1) return PLM_ERR_SHAPE;
-    if (!p0) return PLM_ERR_SHAPE;
+    if (mode != DECAY_GIVEN && !p0) return PLM_ERR_SHAPE;
     if (N > 256) return PLM_ERR_UNSUPPORTED;
     if (max_segs > 1 && (!seg_state || !seg_decay || seg_len <= 0 || max_segs > 65535)) return PLM_ERR_SHAPE;
     ScanArgs a;
@@ -413,6 +595,9 @@ extern "C" int plm_linear_scan(const void* q, const void* k, const void* v, cons
     a.n_seqs = n_seqs, a.H = H, a.N = N, a.P = P, a.heads_per_group = heads_per_group;
     a.seg_len = seg_len, a.max_segs = max_segs < 1 ? 1 : max_segs;
     a.seg_state = seg_state, a.seg_decay = seg_decay;
+    const auto al = [](const void* p_, long ld, int bytes) { return (uintptr_t)p_ % 16 == 0 && (ld * bytes) % 16 == 0; };
+    a.vec8 = dtype == PLM_BF16 && N % 8 == 0 && P % 8 == 0 && al(q, ldq, 2) && al(k, ldk, 2) && al(v, ldv, 2) &&
+             (mode == DECAY_STEP || (mode == DECAY_GIVEN ? al(raw, ldraw, 4) : al(raw, ldraw, 2)));
     if (dtype == PLM_F32) return scan_dispatch<float>(a, mode, stream);
     if (dtype == PLM_BF16) return scan_dispatch<bf16>(a, mode, stream);
     return PLM_ERR_DTYPE;
@@ -507,49 +692,59 @@ extern "C" int plm_gated_norm(const void* x, int x_dtype, long ldx, const void* 
 
 // ------------------------------------------------------------------------------------------------ one matrix per head
 // out[t, h, o] = sum_i W[h][o][i] * x[t, h, i], optionally times sigmoid(gate[t, h, o]).  x [T, H * I] with row stride
-// ldx, W [H, O, I], out [T, H * O].  Tiles of 16 tokens x 64 outputs, the inputs walked 32 at a time through shared
-// memory, sums in fp32 in ascending order of i.
-#define HL_TT 16
+// ldx, W [H, O, I], out [T, H * O].  Tiles of 64 tokens x 64 outputs, 4 x 4 of them a thread, the inputs walked 32 at
+// a time through shared memory, sums in fp32 in ascending order of i.
+#define HL_TT 64
 #define HL_TO 64
 #define HL_TI 32
 template <typename T>
 __global__ void __launch_bounds__(256) head_linear_kernel(const T* __restrict__ x, long ldx, const T* __restrict__ W,
                                                           const T* __restrict__ gate, long ldg, T* __restrict__ out, long ldo,
                                                           int n_tokens, int H, int O, int I) {
-    __shared__ float xs[HL_TT][HL_TI + 1];
-    __shared__ float ws[HL_TO][HL_TI + 1];
+    __shared__ float xs[HL_TI][HL_TT + 4];                 // transposed: a thread reads its 4 tokens as one float4
+    __shared__ float ws[HL_TI][HL_TO + 4];
     pdl_launch_dependents();
     const int h = blockIdx.z, t0 = blockIdx.y * HL_TT, o0 = blockIdx.x * HL_TO;
-    const int ol = threadIdx.x % HL_TO, tg = threadIdx.x / HL_TO;          // 4 token groups of 4 tokens each
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    const int og = threadIdx.x % 16, tg = threadIdx.x / 16;               // 4 outputs x 4 tokens a thread
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
     pdl_wait();
     for (int i0 = 0; i0 < I; i0 += HL_TI) {
         __syncthreads();
         for (int idx = threadIdx.x; idx < HL_TT * HL_TI; idx += 256) {
             const int tt = idx / HL_TI, ii = idx % HL_TI;
-            xs[tt][ii] = (t0 + tt < n_tokens && i0 + ii < I) ? to_f32<T>(x[(long)(t0 + tt) * ldx + (long)h * I + i0 + ii]) : 0.f;
+            xs[ii][tt] = (t0 + tt < n_tokens && i0 + ii < I) ? to_f32<T>(x[(long)(t0 + tt) * ldx + (long)h * I + i0 + ii]) : 0.f;
         }
         for (int idx = threadIdx.x; idx < HL_TO * HL_TI; idx += 256) {
             const int oo = idx / HL_TI, ii = idx % HL_TI;
-            ws[oo][ii] = (o0 + oo < O && i0 + ii < I) ? to_f32<T>(W[((long)h * O + o0 + oo) * I + i0 + ii]) : 0.f;
+            ws[ii][oo] = (o0 + oo < O && i0 + ii < I) ? to_f32<T>(W[((long)h * O + o0 + oo) * I + i0 + ii]) : 0.f;
         }
         __syncthreads();
 #pragma unroll 8
         for (int ii = 0; ii < HL_TI; ++ii) {
-            const float wv = ws[ol][ii];
+            const float4 xv = *(const float4*)&xs[ii][tg * 4];
+            const float4 wv = *(const float4*)&ws[ii][og * 4];
+            const float xr[4] = {xv.x, xv.y, xv.z, xv.w}, wr[4] = {wv.x, wv.y, wv.z, wv.w};
 #pragma unroll
-            for (int j = 0; j < 4; ++j) acc[j] = fmaf(wv, xs[tg * 4 + j][ii], acc[j]);
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(wr[j], xr[i], acc[i][j]);
         }
     }
-    if (o0 + ol < O) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int t = t0 + tg * 4 + i;
+        if (t >= n_tokens) continue;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            const int t = t0 + tg * 4 + j;
-            if (t < n_tokens) {
-                float val = acc[j];
-                if (gate) val *= sigmoid_f(to_f32<T>(gate[(long)t * ldg + (long)h * O + o0 + ol]));
-                out[(long)t * ldo + (long)h * O + o0 + ol] = from_f32<T>(val);
-            }
+            const int o = o0 + og * 4 + j;
+            if (o >= O) continue;
+            float val = acc[i][j];
+            if (gate) val *= sigmoid_f(to_f32<T>(gate[(long)t * ldg + (long)h * O + o]));
+            out[(long)t * ldo + (long)h * O + o] = from_f32<T>(val);
         }
     }
 }

@@ -9,7 +9,7 @@ import torch
 
 from ._lib import PAGE_TOKENS, KernelError, _check, _dev, _dt, _fn, _i32, _p, _stream, set_bounds
 
-DECAY_STEP, DECAY_SIGMOID = 1, 2
+DECAY_STEP, DECAY_SIGMOID, DECAY_GIVEN = 1, 2, 3
 
 
 def _cols(t: torch.Tensor, name: str) -> int:
@@ -31,12 +31,15 @@ def _f32(t: Optional[torch.Tensor], name: str, numel: int) -> None:
 
 def causal_conv(u: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor, step) -> torch.Tensor:
     """Depthwise causal convolution over each sequence's tokens followed by SiLU.  `u` [T, C] (a column slice
-    will do), `weight` [C, taps] float32 with the current token's tap last, `bias` [C] float32 or None, `state`
+    will do), `weight` [taps, C] float32 (tap-major: a checkpoint's [C, taps] transposed) with the current token's
+    tap last, `bias` [C] float32 or None, `state`
     float32 [slots, >= (taps - 1) * C] with contiguous rows: the last taps - 1 inputs of every sequence, oldest
     first; it is read for the tokens before the step's first and brought up to date.  Returns [T, C] like u."""
     ldu = _cols(u, "u")
     T, C = u.shape
-    taps = weight.shape[1]
+    taps = weight.shape[0]
+    if weight.dim() != 2 or weight.shape[1] != C:
+        raise KernelError(f"causal_conv: the weights must be [taps, {C}], got {tuple(weight.shape)}")
     _f32(weight, "weight", C * taps), _f32(bias, "bias", C)
     lds = _cols(state, "state")
     if state.dtype != torch.float32 or state.shape[1] < (taps - 1) * C:
@@ -96,15 +99,24 @@ def linear_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, raw: torch.Te
     # state, a small kernel chains those into the state at every segment's start, a second pass gives y.
     seg_len, n_segs = scan_plan(step.n_seqs, H, N, P, step.max_new)
     seg_state = seg_decay = None
+    kernels, run_mode = 1, mode
     if n_segs > 1:
         seg_state = torch.empty((step.n_seqs, n_segs, H * N * P), dtype=torch.float32, device=v.device)
         seg_decay = torch.empty((step.n_seqs, n_segs, H * N), dtype=torch.float32, device=v.device)
+        kernels = 3
+        if mode == DECAY_SIGMOID:
+            # both passes want the decays: their exponentials are taken once, by a kernel of their own
+            given = torch.empty((T, H * N), dtype=torch.float32, device=v.device)
+            _check(_fn("recurrent", "plm_sigmoid_decay")(_p(raw), _dt(raw, "raw"), ldr, _p(p0), float(power), _p(given), T,
+                                                         H * N, _stream()), f"sigmoid_decay T={T} C={H * N}",
+                   nbytes=T * H * N * (4 + raw.element_size()))
+            raw, ldr, run_mode = given, H * N, DECAY_GIVEN
     _check(_fn("recurrent", "plm_linear_scan")(
-        _p(q), _p(k), _p(v), _p(raw), _dt(v, "v"), ldq, ldk, ldv, ldr, mode, _p(p0), _p(p1), _p(skip), float(q_scale),
+        _p(q), _p(k), _p(v), _p(raw), _dt(v, "v"), ldq, ldk, ldv, ldr, run_mode, _p(p0), _p(p1), _p(skip), float(q_scale),
         float(power), _p(state), lds, _p(y), H * P, _p(step.seq_start), _p(step.seq_slot), step.n_seqs, H, N, P,
         heads_per_group, seg_len, n_segs, _p(seg_state), _p(seg_decay), _stream()),
         f"linear_scan T={T} H={H} N={N} P={P}" + (f" in {n_segs} segments" if n_segs > 1 else ""),
-        kernels=3 if n_segs > 1 else 1,
+        kernels=kernels,
         nbytes=T * (2 * G * N + H * P) * v.element_size() + T * H * P * 4 + 2 * step.n_seqs * H * N * P * 4,
         flops=(10 if n_segs > 1 else 6) * T * H * N * P)
     return y

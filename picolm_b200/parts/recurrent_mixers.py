@@ -61,7 +61,8 @@ class Mamba2(_StateMixer):
 
     def load(self, tensors):
         self.w_in, self.w_o = tensors["in"], tensors["o"]
-        self.conv_w, self.conv_b = self._f32(tensors["conv"]), self._f32(tensors["conv.b"])
+        # the kernel wants the taps' weights tap by tap, neighbouring channels side by side
+        self.conv_w, self.conv_b = self._f32(tensors["conv"].to(torch.float32).t()), self._f32(tensors["conv.b"])
         self.dt_bias, self.a_log, self.skip = self._f32(tensors["dt_bias"]), self._f32(tensors["A_log"]), self._f32(tensors["D"])
         self.norm_w = self._f32(tensors["norm"])
 

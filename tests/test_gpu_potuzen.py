@@ -102,24 +102,27 @@ class _Step:
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("taps", [1, 2, 4])
-def test_causal_conv_kernel(dtype, taps):
+@pytest.mark.parametrize("C", [37, 48])            # 48: bfloat16 channels in eights, the vectorised kernel
+def test_causal_conv_kernel(dtype, taps, C):
     """Ragged prompts, then portions that are shorter than the taps, then single tokens: the state carries over."""
     from picolm_b200 import ops
-    dev, C = "cuda:0", 37
+    dev = "cuda:0"
     g = torch.Generator().manual_seed(taps)
     lens = [9, 1, 2]
     total = [n + 2 + 1 + 3 for n in lens]
-    u = [torch.randn(n, C + 5, generator=g).to(dtype) for n in total]           # column slices of a wider matrix
+    pad = 5 if C % 8 else 16                                                      # column slices of a wider matrix
+    u = [torch.randn(n, C + pad, generator=g).to(dtype) for n in total]
     w = torch.randn(C, taps, generator=g)
     b = torch.randn(C, generator=g)
-    want = [P.silu(P.causal_conv(x[:, 2:2 + C].double(), w.double(), b.double())) for x in u]
+    lo = 2 if C % 8 else 8
+    want = [P.silu(P.causal_conv(x[:, lo:lo + C].double(), w.double(), b.double())) for x in u]
     state = torch.zeros(5, (taps - 1) * C + 3, device=dev)                        # rows wider than the state
     slots = [3, 0, 2]
     got, at = [[] for _ in lens], [0, 0, 0]
     for cut in ([9, 1, 2], [2, 2, 2], [1, 1, 1], [3, 3, 3]):
         step = _Step(cut, slots, dev)
         rows = torch.cat([u[i][at[i]:at[i] + n] for i, n in enumerate(cut)]).to(dev)
-        out = ops.causal_conv(rows[:, 2:2 + C], w.to(dev), b.to(dev), state[:, :(taps - 1) * C], step)
+        out = ops.causal_conv(rows[:, lo:lo + C], w.t().contiguous().to(dev), b.to(dev), state[:, :(taps - 1) * C], step)
         o = 0
         for i, n in enumerate(cut):
             got[i].append(out[o:o + n].float().cpu())
@@ -134,7 +137,8 @@ def test_causal_conv_kernel(dtype, taps):
 @pytest.mark.parametrize("N,P_,H,hpg,lens,cuts", [
     (8, 12, 6, 2, [23, 4], ([7, 1], [1, 1], [15, 2])), (5, 33, 2, 1, [23, 4], ([7, 1], [1, 1], [15, 2])),
     (48, 64, 4, 4, [23, 4], ([7, 1], [1, 1], [15, 2])), (130, 8, 1, 1, [23, 4], ([7, 1], [1, 1], [15, 2])),
-    (20, 36, 2, 2, [521, 270], ([200, 3], [1, 1], [320, 266]))])
+    (20, 36, 2, 2, [521, 270], ([200, 3], [1, 1], [320, 266])),
+    (16, 64, 2, 1, [521, 270], ([200, 3], [1, 1], [320, 266]))])        # sizes in eights: bfloat16 rows are read 16 bytes at a time
 def test_linear_scan_kernel(mode, N, P_, H, hpg, lens, cuts):
     """The recurrence alone against a loop over tokens, cut into steps of several sizes (one token included), with
     key sizes that are no multiple of four and value sizes that are no multiple of the tile; the long case runs in
@@ -145,15 +149,16 @@ def test_linear_scan_kernel(mode, N, P_, H, hpg, lens, cuts):
     dev = "cuda:0"
     g = torch.Generator().manual_seed(N * 7 + P_)
     G = H // hpg
-    q = [torch.randn(n, G * N, generator=g) for n in lens]
-    k = [torch.randn(n, G * N, generator=g) for n in lens]
-    v = [torch.randn(n, H * P_, generator=g) for n in lens]
+    dt = torch.bfloat16 if (N, P_) == (16, 64) else torch.float32
+    q = [torch.randn(n, G * N, generator=g).to(dt) for n in lens]
+    k = [torch.randn(n, G * N, generator=g).to(dt) for n in lens]
+    v = [torch.randn(n, H * P_, generator=g).to(dt) for n in lens]
     if mode == "step":
-        raw = [torch.randn(n, H, generator=g) for n in lens]
+        raw = [torch.randn(n, H, generator=g).to(dt) for n in lens]
         p0, p1, skip = torch.randn(H, generator=g), torch.randn(H, generator=g) - 1.0, torch.randn(H, generator=g)
         power, q_scale = 1.0, 1.0
     else:
-        raw = [torch.randn(n, H * N, generator=g) * 2 for n in lens]
+        raw = [(torch.randn(n, H * N, generator=g) * 2).to(dt) for n in lens]
         p0, p1, skip = torch.randn(H * N, generator=g) + 2.0, None, None
         power, q_scale = 1.0 / 3.0, N ** -0.5
 
