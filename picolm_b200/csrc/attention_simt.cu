@@ -18,9 +18,11 @@
 namespace {
 
 constexpr int WARPS = 4;
-constexpr int MAX_HD = 256;            // acc registers per lane: MAX_HD / 32
+constexpr int MAX_HD = 1024;           // the largest head size; acc registers per lane: MAX_HD / 32 of the instance
 
-template <typename Ta, typename Tc>
+// MAX_HD: the instance's largest head size (256 for the usual heads; 512 and 1024 for the wide single head of a
+// latent cache, whose keys are the latents themselves).
+template <typename Ta, typename Tc, int MAX_HD>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_rows_kernel(const Ta* __restrict__ q, const Tc* __restrict__ kc, const Tc* __restrict__ vc,
                       Ta* __restrict__ out, const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
@@ -96,15 +98,23 @@ extern "C" int plm_attention_rows(const void* q, const void* kc, const void* vc,
     if (H <= 0 || G <= 0 || H % G || hd <= 0 || hd > MAX_HD) return PLM_ERR_SHAPE;
     dim3 grid(n_tokens, (H + WARPS - 1) / WARPS);
     const size_t smem = (size_t)WARPS * hd * sizeof(float);
+#define ROWS_LAUNCH(Ta_, MAXHD_)                                                                                       \
+    attention_rows_kernel<Ta_, Ta_, MAXHD_><<<grid, WARPS * 32, smem, stream>>>(                                       \
+        (const Ta_*)q, (const Ta_*)kc, (const Ta_*)vc, (Ta_*)out, tok_pos, tok_seq, block_table, max_pages, H, G, hd, \
+        scale, window)
+#define ROWS_BY_SIZE(Ta_)                          \
+    do {                                           \
+        if (hd <= 256) ROWS_LAUNCH(Ta_, 256);      \
+        else if (hd <= 512) ROWS_LAUNCH(Ta_, 512); \
+        else ROWS_LAUNCH(Ta_, 1024);               \
+    } while (0)
     if (dtype == PLM_F32)
-        attention_rows_kernel<float, float><<<grid, WARPS * 32, smem, stream>>>(
-            (const float*)q, (const float*)kc, (const float*)vc, (float*)out, tok_pos, tok_seq, block_table, max_pages,
-            H, G, hd, scale, window);
+        ROWS_BY_SIZE(float);
     else if (dtype == PLM_BF16)
-        attention_rows_kernel<bf16, bf16><<<grid, WARPS * 32, smem, stream>>>(
-            (const bf16*)q, (const bf16*)kc, (const bf16*)vc, (bf16*)out, tok_pos, tok_seq, block_table, max_pages, H,
-            G, hd, scale, window);
+        ROWS_BY_SIZE(bf16);
     else
         return PLM_ERR_DTYPE;
+#undef ROWS_BY_SIZE
+#undef ROWS_LAUNCH
     return plm_launch_status();
 }

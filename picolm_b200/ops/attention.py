@@ -21,8 +21,8 @@ def attention_rows(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor
     G = num_kv_heads
     if k_cache.dtype != q.dtype or k_cache.shape[1:] != (G, PAGE_TOKENS, hd) or v_cache.shape != k_cache.shape:
         raise KernelError(f"attention: the cache must be [pages, {G}, {PAGE_TOKENS}, {hd}] of {q.dtype}")
-    if hd > 256:
-        raise KernelError(f"attention: head_dim {hd} exceeds 256, the largest this kernel takes")
+    if hd > 1024:
+        raise KernelError(f"attention: head_dim {hd} exceeds 1024, the largest this kernel takes")
     if out is None:
         out = torch.empty((T, H * hd), dtype=q.dtype, device=q.device)
     _cache_bounds("attention_simt", (), k_cache, block_table)

@@ -282,6 +282,7 @@ ALONE = {
     "latent": [_latent(), _latent(heads=1, dim=16, vdim=4, kv_rank=16, q_rank=8, window=70, scale=0.25)],
     "latent_window_1": [_latent(window=1)],
     "latent_wide_window": [_latent(window=1000, kv_rank=32)],
+    "latent_wide_rank": [_latent(kv_rank=300, q_rank=40, heads=2)],          # a latent wider than any head the library had
     "mamba2": [_mamba(), _mamba(heads=4, vdim=8, state=16, groups=1, conv=4, norm_groups=1)],
     "mamba2_groups_are_heads": [_mamba(heads=2, vdim=40, state=6, groups=2, conv=2, norm_groups=4)],
     "gla": [_gla(), _gla(heads=3, dim=8, vdim=8, tau=1.0, decay_rank=2)],
@@ -412,3 +413,33 @@ def test_greedy_generation_through_the_entry_point(tmp_path):
     assert stats.batches == 3 and eng.cache.slots.used == 0
     assert eng.use_graphs, "decode steps of this design are meant to replay captured graphs"
     eng.cache.check()
+
+
+def test_trace_replay_as_a_user_runs_it(tmp_path):
+    """bin/trace_run on a Potuzen folder: a batch of unequal prompts, single tokens until the shorter requests end,
+    a request alone afterwards in the slot that was given back; more requests of a few tokens than the token count
+    alone would give pages for."""
+    from test_gpu_trace_run import Replay
+    d, tensors, config = _make(tmp_path, "replay", _config(MIXED), seed=17)
+    reqs = {f"q{i}": random_tokens(n, 97, 300 + i) for i, n in enumerate([70, 9, 1, 30, 3, 2])}
+    ref = {k: _plain(tensors, config, t) for k, t in reqs.items()}
+    rp = Replay(d, "float32", str(tmp_path / "out"), max_tokens=128)
+    try:
+        batch = ["q0", "q1", "q2", "q4", "q5"]
+        pos = {"q0": 50, "q1": 4, "q2": 1, "q4": 2, "q5": 1}
+        got = rp.send([{"id": k, "tokens": reqs[k][:pos[k]], "want": [pos[k] - 1]} for k in batch],
+                      end=[k for k in batch if pos[k] == len(reqs[k])])
+        for row, k in enumerate(batch):
+            _close(got[row:row + 1], ref[k][pos[k] - 1:pos[k]], what=f"prompt of {k}")
+        live = [k for k in batch if pos[k] < len(reqs[k])]
+        while live:
+            ending = [k for k in live if pos[k] + 1 == len(reqs[k])]
+            got = rp.send([{"id": k, "tokens": [reqs[k][pos[k]]], "want": [0]} for k in live], end=ending)
+            for row, k in enumerate(live):
+                _close(got[row:row + 1], ref[k][pos[k]:pos[k] + 1], what=f"{k} at {pos[k]}")
+                pos[k] += 1
+            live = [k for k in live if pos[k] < len(reqs[k])]
+        got = rp.send([{"id": "again", "tokens": reqs["q3"], "want": [0, 29]}], end=["again"])
+        _close(got, ref["q3"][[0, 29]], what="alone, afterwards")
+    finally:
+        rp.close()
