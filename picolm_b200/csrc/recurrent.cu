@@ -749,12 +749,61 @@ __global__ void __launch_bounds__(256) head_linear_kernel(const T* __restrict__ 
     }
 }
 
+// The same for a handful of tokens (a decode step): the weights are what has to be read, once.  One warp per output
+// row (h, o): it takes the row's I weights into registers (up to 32 a lane) and forms the dot product with every
+// token's x[t, h, :]; a lane's elements are I / 32 apart so that the warp's loads are contiguous.
+#define HLS_MAX_T 16
+template <typename T>
+__global__ void __launch_bounds__(256) head_linear_small_kernel(const T* __restrict__ x, long ldx, const T* __restrict__ W,
+                                                                const T* __restrict__ gate, long ldg, T* __restrict__ out,
+                                                                long ldo, int n_tokens, int H, int O, int I) {
+    pdl_launch_dependents();
+    const long row = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;          // h * O + o
+    const int lane = threadIdx.x & 31;
+    if (row >= (long)H * O) return;
+    const int h = (int)(row / O);
+    float wr[32];
+    const T* wp = W + row * I;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+        const int c = lane + 32 * i;
+        wr[i] = c < I ? to_f32<T>(wp[c]) : 0.f;
+    }
+    pdl_wait();
+    for (int t = 0; t < n_tokens; ++t) {
+        const T* xr = x + (long)t * ldx + (long)h * I;
+        float acc = 0.f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            const int c = lane + 32 * i;
+            if (c < I) acc = fmaf(wr[i], to_f32<T>(xr[c]), acc);
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) {
+            if (gate) acc *= sigmoid_f(to_f32<T>(gate[(long)t * ldg + row]));
+            out[(long)t * ldo + row] = from_f32<T>(acc);
+        }
+    }
+}
+
 extern "C" int plm_head_linear(const void* x, int dtype, long ldx, const void* W, const void* gate, long ldg, void* out, long ldo,
                                int n_tokens, int H, int O, int I, cudaStream_t stream) {
     if (n_tokens <= 0 || H <= 0 || O <= 0 || I <= 0 || H > 65535) return PLM_ERR_SHAPE;
+    cudaError_t e;
+    if (n_tokens <= HLS_MAX_T && I <= 1024) {
+        const unsigned blocks = (unsigned)(((long)H * O * 32 + 255) / 256);
+        if (dtype == PLM_F32)
+            e = launch_pdl(head_linear_small_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)x, ldx, (const float*)W,
+                           (const float*)gate, ldg, (float*)out, ldo, n_tokens, H, O, I);
+        else if (dtype == PLM_BF16)
+            e = launch_pdl(head_linear_small_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (const bf16*)x, ldx, (const bf16*)W,
+                           (const bf16*)gate, ldg, (bf16*)out, ldo, n_tokens, H, O, I);
+        else
+            return PLM_ERR_DTYPE;
+        return plm_status_of(e);
+    }
     const dim3 grid((O + HL_TO - 1) / HL_TO, (n_tokens + HL_TT - 1) / HL_TT, H);
     if (grid.y > 65535) return PLM_ERR_SHAPE;
-    cudaError_t e;
     if (dtype == PLM_F32)
         e = launch_pdl(head_linear_kernel<float>, grid, dim3(256), 0, stream, (const float*)x, ldx, (const float*)W, (const float*)gate,
                        ldg, (float*)out, ldo, n_tokens, H, O, I);

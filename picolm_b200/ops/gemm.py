@@ -20,8 +20,11 @@ def _work(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, extra: int = 0) -
 
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype,
               out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """out[M, N] = a[M, K] @ w[N, K]^T on the CUDA cores, fp32 accumulation."""
-    _dev(a, "a"), _dev(w, "w")
+    """out[M, N] = a[M, K] @ w[N, K]^T on the CUDA cores, fp32 accumulation.  `a` may be a slice of columns of a
+    wider matrix (rows contiguous, any row stride)."""
+    if not (a.is_cuda and a.dim() == 2 and a.stride(1) == 1 and a.stride(0) >= a.shape[1]):
+        _dev(a, "a")
+    _dev(w, "w")
     M, K = a.shape
     N, K2 = w.shape
     if K != K2:
@@ -29,7 +32,7 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype,
     if out is None:
         out = torch.empty((M, N), dtype=out_dtype, device=a.device)
     _check(_fn("gemm_simt", "plm_gemm_simt")(
-        _p(a), _dt(a, "a"), _p(w), _dt(w, "w"), _p(out), _dt(out, "out"), M, N, K, K, K, N, _stream()),
+        _p(a), _dt(a, "a"), _p(w), _dt(w, "w"), _p(out), _dt(out, "out"), M, N, K, a.stride(0), K, N, _stream()),
         f"gemm_simt {M}x{N}x{K}", **_work(a, w, out))
     return out
 

@@ -136,7 +136,9 @@ class GatedLinearAttention(_StateMixer):
         proj = ops.linear(h, self.w_h, dt)
         q, k, v = proj[:, :HN], proj[:, HN:2 * HN], proj[:, 2 * HN:2 * HN + HP]
         g, a1 = proj[:, 2 * HN + HP:2 * HN + 2 * HP], proj[:, 2 * HN + 2 * HP:]
-        z = ops.linear(a1.contiguous(), self.w_a2, dt)
+        # the bottleneck is a few columns wide: the CUDA-core product reads them where they lie; a wide one is copied
+        # out for the tensor cores
+        z = ops.gemm_simt(a1, self.w_a2, dt) if a1.shape[1] < 64 else ops.linear(a1.contiguous(), self.w_a2, dt)
         o = ops.linear_scan(q=q, k=k, v=v, raw=z, mode=ops.DECAY_SIGMOID, p0=self.a2_bias, p1=None, skip=None,
                             q_scale=self.N ** -0.5, power=1.0 / self.tau, state=cache.state, step=step, heads=self.H,
                             key_dim=self.N, value_dim=self.P)

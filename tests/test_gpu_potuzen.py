@@ -225,14 +225,22 @@ def test_gated_norm_and_head_linear_kernels():
     got = ops.gated_norm(x.to(torch.bfloat16), torch.bfloat16, weight=w_all, eps=1e-3)
     assert torch.allclose(got.double().cpu(), P.rms_norm(x.to(torch.bfloat16).double().cpu(), w_all.double().cpu(), 1e-3),
                           atol=3e-2, rtol=1e-2)
-    # one small matrix per head, sizes that fill no tile, with and without the sigmoid gate
-    H, O, I, T = 3, 70, 37, 21
-    xs, W = torch.randn(T, H * I + 2, generator=g).to(dev), torch.randn(H, O, I, generator=g).to(dev)
-    gt = torch.randn(T, H * O, generator=g).to(dev)
-    want = torch.einsum("hoi,thi->tho", W.double().cpu(), xs[:, 2:].double().cpu().view(T, H, I)).reshape(T, H * O)
-    assert torch.allclose(ops.head_linear(xs[:, 2:], W).double().cpu(), want, atol=1e-4, rtol=1e-5)
-    assert torch.allclose(ops.head_linear(xs[:, 2:], W, gate=gt).double().cpu(), want * torch.sigmoid(gt.double().cpu()),
-                          atol=1e-4, rtol=1e-5)
+    # groups wider than a warp keeps in registers: the kernel that reads them twice
+    wide2 = torch.randn(3, 1200, generator=g).to(dev)
+    w600 = torch.randn(600, generator=g).to(dev)
+    got = ops.gated_norm(wide2, torch.float32, weight=w600, eps=1e-3, group=600, weight_per_group=True)
+    want = P.rms_norm(wide2.double().cpu().view(3, 2, 600), w600.double().cpu(), 1e-3).reshape(3, 1200)
+    assert torch.allclose(got.double().cpu(), want, atol=1e-5, rtol=1e-5)
+    # one small matrix per head, sizes that fill no tile, with and without the sigmoid gate; a prompt's many tokens
+    # and a decode step's few go through different kernels
+    for T in (21, 5):
+        H, O, I = 3, 70, 37
+        xs, W = torch.randn(T, H * I + 2, generator=g).to(dev), torch.randn(H, O, I, generator=g).to(dev)
+        gt = torch.randn(T, H * O, generator=g).to(dev)
+        want = torch.einsum("hoi,thi->tho", W.double().cpu(), xs[:, 2:].double().cpu().view(T, H, I)).reshape(T, H * O)
+        assert torch.allclose(ops.head_linear(xs[:, 2:], W).double().cpu(), want, atol=1e-4, rtol=1e-5)
+        assert torch.allclose(ops.head_linear(xs[:, 2:], W, gate=gt).double().cpu(), want * torch.sigmoid(gt.double().cpu()),
+                              atol=1e-4, rtol=1e-5)
 
 
 def test_closing_norm_add_and_opening_norm_in_one_kernel():
@@ -282,7 +290,9 @@ ALONE = {
     "latent": [_latent(), _latent(heads=1, dim=16, vdim=4, kv_rank=16, q_rank=8, window=70, scale=0.25)],
     "latent_window_1": [_latent(window=1)],
     "latent_wide_window": [_latent(window=1000, kv_rank=32)],
-    "latent_wide_rank": [_latent(kv_rank=300, q_rank=40, heads=2)],          # a latent wider than any head the library had
+    # a latent wider than any head the library had (a small scale keeps the scores, sums over 300 products of
+    # scaled-up maps, where float32 resolves them to the tolerance)
+    "latent_wide_rank": [_latent(kv_rank=300, q_rank=40, heads=2, scale=0.03)],
     "mamba2": [_mamba(), _mamba(heads=4, vdim=8, state=16, groups=1, conv=4, norm_groups=1)],
     "mamba2_groups_are_heads": [_mamba(heads=2, vdim=40, state=6, groups=2, conv=2, norm_groups=4)],
     "gla": [_gla(), _gla(heads=3, dim=8, vdim=8, tau=1.0, decay_rank=2)],
