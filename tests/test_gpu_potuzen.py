@@ -295,6 +295,7 @@ ALONE = {
     "latent_wide_rank": [_latent(kv_rank=300, q_rank=40, heads=2, scale=0.03)],
     "mamba2": [_mamba(), _mamba(heads=4, vdim=8, state=16, groups=1, conv=4, norm_groups=1)],
     "mamba2_groups_are_heads": [_mamba(heads=2, vdim=40, state=6, groups=2, conv=2, norm_groups=4)],
+    "mamba2_one_tap": [_mamba(conv=1), _mamba(heads=3, vdim=8, state=40, groups=1, conv=7, norm_groups=3)],
     "gla": [_gla(), _gla(heads=3, dim=8, vdim=8, tau=1.0, decay_rank=2)],
     "no_feed_forward": [dict(_gla(), mlp=None), dict(_latent(), mlp=None), dict(_mamba(), mlp=None)],
     "mixed": MIXED,
@@ -398,6 +399,71 @@ def test_bfloat16_follows_the_plain_implementation(tmp_path):
         rel = ((got - whole).double().pow(2).mean().sqrt() / want.double().std()).item()
         assert rel < 0.03, f"two cuts of the same request differ by {rel:.3f} of the spread"
     eng.cache.check()
+
+
+@pytest.mark.parametrize("R,H,window", [(64, 3, 33), (128, 2, 64), (32, 5, 65), (80, 1, 9), (256, 2, 130), (48, 4, 1), (24, 3, 70)])
+def test_attention_over_a_latent_cache_at_the_window_edge(R, H, window):
+    """What the latent attention asks of the library's bfloat16 attention kernels (the tcgen05 prompt kernel at 64
+    and 128, the mma.sync prompt and decode kernels at other multiples of 16, the CUDA cores otherwise): H query heads
+    over ONE kv head whose values are its keys, behind a window, in pages that are out of order.  Every query is
+    aimed at one key with a score that dwarfs the others: even rows at the last key inside the window, odd rows at
+    the first key outside it, which must not be seen.  A portion of a prompt after a cached prefix, then single tokens."""
+    from picolm_b200 import ops
+    from picolm_b200.cache.sequence_cache import KVLayerCache
+    dev = "cuda:0"
+    g = torch.Generator().manual_seed(R + window)
+    L, start = 230, 100
+    c = torch.randn(L, R, generator=g).to(torch.bfloat16)
+    n_pages = (L + 63) // 64
+    order = [3, 1, 4, 2][:n_pages]
+    pages = torch.zeros(6, 1, 64, R, dtype=torch.bfloat16)
+    pages[0] = 7.0                                                   # the null page holds what nobody may read
+    for b_, pg in enumerate(order):
+        chunk = c[b_ * 64:(b_ + 1) * 64]
+        pages[pg, 0, :chunk.shape[0]] = chunk
+    pages = pages.to(dev)
+    scale = 0.5
+
+    def queries(positions):
+        q = torch.zeros(len(positions), H, R)
+        for r, i in enumerate(positions):
+            target = i - window + 1 if r % 2 == 0 else i - window
+            target = min(max(target, 0), i)
+            for h in range(H):
+                # along the target's latent, long enough that its score stands 30 above an ordinary key's
+                q[r, h] = c[target].float() * (30.0 + 4 * h) / (scale * c[target].float().pow(2).sum())
+        return q.to(torch.bfloat16)
+
+    def plain(q, positions):
+        out = torch.zeros(len(positions), H, R, dtype=torch.float64)
+        cd = c.double()
+        for r, i in enumerate(positions):
+            lo = max(0, i - window + 1)
+            sc = (q[r].double() @ cd[lo:i + 1].T) * scale
+            out[r] = torch.softmax(sc, dim=-1) @ cd[lo:i + 1]
+        return out.reshape(len(positions), H * R)
+
+    def check(got, want, what):
+        err = (got.double().cpu() - want).abs().max().item()
+        assert err <= 0.03 * want.abs().max().item(), f"{what}: max |diff| {err:.3f} of values up to {want.abs().max():.2f}"
+
+    table = torch.tensor([order + [0] * (5 - len(order))], dtype=torch.int32, device=dev)
+    # a portion of a prompt: positions start .. L - 1 of one sequence whose first `start` positions are cached
+    pos = list(range(start, L))
+    step = _Step([len(pos)], [0], dev, starts=[start])
+    step.seq_kv_len = torch.tensor([L], dtype=torch.int32, device=dev)
+    step.max_position = L - 1
+    q = queries(pos)
+    kv = KVLayerCache(pages, pages, table, window, True)
+    check(ops.attention(q.to(dev), kv, step, 1, scale), plain(q, pos), "portion of a prompt")
+    # single tokens: four sequences on the same pages at different lengths (one ends on a page's first position)
+    pos = [L - 1, 128, 191, 70]
+    step = _Step([1] * 4, [0, 1, 2, 3], dev, starts=pos)
+    step.seq_kv_len = torch.tensor([p_ + 1 for p_ in pos], dtype=torch.int32, device=dev)
+    step.max_position = max(pos)
+    q = queries(pos)
+    kv = KVLayerCache(pages, pages, table.repeat(4, 1).contiguous(), window, True)
+    check(ops.attention(q.to(dev), kv, step, 1, scale), plain(q, pos), "single tokens")
 
 
 # ---------------------------------------------------------------------------------------------- generation
