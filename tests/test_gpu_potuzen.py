@@ -299,12 +299,15 @@ ALONE = {
     "gla": [_gla(), _gla(heads=3, dim=8, vdim=8, tau=1.0, decay_rank=2)],
     "no_feed_forward": [dict(_gla(), mlp=None), dict(_latent(), mlp=None), dict(_mamba(), mlp=None)],
     "mixed": MIXED,
+    # a width that is no multiple of 4 (the fused norm kernel refuses it, the two norm kernels run) nor of 8 (no tensor map)
+    "odd_width": [_latent(), _mamba(), _gla()],
 }
+WIDTHS = {"odd_width": 42}
 
 
 @pytest.mark.parametrize("name", sorted(ALONE))
 def test_float32_model_matches_plain_in_every_cut(tmp_path, name):
-    d, tensors, config = _make(tmp_path, name, _config(ALONE[name]), seed=len(name))
+    d, tensors, config = _make(tmp_path, name, _config(ALONE[name], width=WIDTHS.get(name, 40)), seed=len(name))
     eng = _engine(d)
     a, b, c = random_tokens(150, 97, 1), random_tokens(67, 97, 2), random_tokens(1, 97, 3)
     want = {id(t): _plain(tensors, config, t) for t in (a, b, c)}
