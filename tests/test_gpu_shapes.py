@@ -22,6 +22,7 @@ SHAPES = {
     "mqa_20_heads":  (1, 320, 20, 1,  16, 320, 264, 10000.0, 1e-5, False),      # 20 query heads on one KV head
     "odd_widths":    (2, 72,  3,  3,  24, 100, 97,  10000.0, 1e-5, False),      # F = 100: not a multiple of 8
     "hd40":          (1, 80,  2,  1,  40, 160, 130, 10000.0, 1e-5, False),      # no multiple of 16: CUDA-core attention
+    "hd272":         (1, 64,  1,  1, 272, 64,  50,  10000.0, 1e-5, False),      # wider than the tensor-core kernels take
 }
 
 
@@ -57,15 +58,15 @@ def test_shape_in_every_cut(tmp_path, name, dtype):
         ops.check_status()
 
 
-def test_head_size_beyond_the_kernels_is_refused(tmp_path):
-    """A head of 272 is more than any attention kernel takes: a clear error at the first step, no result."""
-    from picolm_b200.engine import Engine
-    from picolm_b200.ops import KernelError
-    cfg_dict = _config((1, 64, 1, 1, 272, 64, 50, 10000.0, 1e-5, False))
-    d = make_model_dir(str(tmp_path / "hd272"), cfg_dict, 3)
-    for dtype in ("float32", "bfloat16"):
-        eng = Engine.from_folder(d, dtype=dtype, max_tokens=128, max_seqs=1)
-        s = eng.new_sequence()
-        with pytest.raises(KernelError, match="head_dim 272 exceeds 256"):
-            eng.step([(s, [1, 2, 3])])
-        eng.end_sequence(s)
+def test_head_size_beyond_the_kernels_is_refused():
+    """A head of 1,040 is more than any attention kernel takes (the any-size kernel ends at 1,024): a clear error
+    before any launch."""
+    from picolm_b200 import ops
+    dev = "cuda:0"
+    for dt in (torch.float32, torch.bfloat16):
+        q = torch.zeros(2, 1, 1040, dtype=dt, device=dev)
+        cache = torch.zeros(2, 1, 64, 1040, dtype=dt, device=dev)
+        i32 = dict(dtype=torch.int32, device=dev)
+        with pytest.raises(ops.KernelError, match="head_dim 1040 exceeds 1024"):
+            ops.attention_rows(q, cache, cache, torch.tensor([0, 1], **i32), torch.tensor([0, 0], **i32),
+                               torch.tensor([[1]], **i32), 1, 1.0)
