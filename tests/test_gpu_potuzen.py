@@ -522,3 +522,45 @@ def test_trace_replay_as_a_user_runs_it(tmp_path):
         _close(got, ref["q3"][[0, 29]], what="alone, afterwards")
     finally:
         rp.close()
+
+
+def test_command_line(tmp_path):
+    """The library's command line on a Potuzen folder: random weights from a config.json, greedy tokens equal to the plain
+    implementation's, sampling, the per-layer benchmark with a row for every run of the schedule (a layer that shares
+    weights is its owner's second run)."""
+    import re
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    exe = [sys.executable, os.path.join(root, "bin", "picolm_b200")]
+    cfg_path = str(tmp_path / "config.json")
+    with open(cfg_path, "w") as f:
+        json.dump(_config([_latent(window=6), _mamba(), dict(_gla(), mlp=None), dict(_latent(window=6), weights_of=0)]), f)
+    d = str(tmp_path / "model")
+    r = subprocess.run(exe + ["--random-weights", cfg_path, "--out", d, "-s", "3"], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr
+    tensors = P.read_safetensors(os.path.join(d, "model.safetensors"))
+    with open(os.path.join(d, "config.json")) as f:
+        config = json.load(f)
+
+    def greedy(p, n):
+        seq, out = list(p), []
+        for _ in range(n):
+            out.append(int(_plain(tensors, config, seq)[-1].argmax()))
+            seq.append(out[-1])
+        return out
+
+    r = subprocess.run(exe + [d, "-p", "5,6,7; 9", "-n", "6", "-t", "0", "--dtype", "float32", "--stop-id", "-1"],
+                       capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr
+    assert [[int(t) for t in ln.split()] for ln in r.stdout.strip().splitlines()] == [greedy([5, 6, 7], 6), greedy([9], 6)]
+    r = subprocess.run(exe + [d, "-p", "5,6,7; 9", "-n", "6", "-t", "0.8", "-k", "40", "--top-p", "0.9", "-s", "5", "--stop-id", "-1"],
+                       capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr
+    assert [len(ln.split()) for ln in r.stdout.strip().splitlines()] == [6, 6]
+    r = subprocess.run(exe + [d, "-p", "5,6,7,8", "-n", "5", "--benchmark"], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr
+    rows = [ln.split(",") for ln in r.stderr.splitlines() if re.fullmatch(r"\d+,[0-9.]+,[0-9.]+,[0-9.]+,\d+", ln)]
+    assert [int(x[0]) for x in rows] == [0, 1, 2, 0] * 3
+    r = subprocess.run(exe + [d, "--list-tensors"], capture_output=True, text=True, timeout=60)
+    assert "l1.mix.A_log\t[6]\tBF16" in r.stdout and "l3." not in r.stdout
