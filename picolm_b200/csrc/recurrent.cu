@@ -522,17 +522,22 @@ static int scan_dispatch(const ScanArgs& a, int mode, cudaStream_t stream) {
     return plm_status_of(e);
 }
 
-// How a step whose longest sequence brings `max_new` tokens is cut: out[0] tokens per segment, out[1] segments of the
+// How a step of `n_tokens` tokens whose longest sequence brings `max_new` of them is cut: out[0] tokens per segment, out[1] segments of the
 // longest sequence (1: one pass from the cache's state, no scratch memory).  Segments are worth their second pass
 // when the sequences alone leave most of the GPU idle; there are as many as make one wave of blocks (a second, partly
 // filled wave would take as long as the first), each of at least 64 tokens, and no more than keep the scratch memory
 // under 1 GiB.
-extern "C" int plm_linear_scan_plan(int n_seqs, int H, int N, int P, int max_new, int* out) {
+extern "C" int plm_linear_scan_plan(int n_seqs, int H, int N, int P, int max_new, int n_tokens, int* out) {
     out[0] = max_new > 0 ? max_new : 1;
     out[1] = 1;
     if (n_seqs <= 0 || H <= 0 || N <= 0 || P <= 0) return PLM_ERR_SHAPE;
     if (max_new < 192) return PLM_OK;
-    const long blocks = (long)n_seqs * H * ((P + SCAN_PTILE - 1) / SCAN_PTILE);
+    // How many sequences' worth of work there is: the step's tokens over its longest sequence (a captured step
+    // counts padding sequences without tokens among n_seqs, and a short sequence beside a long one fills few blocks).
+    long busy = n_tokens > 0 ? ((long)n_tokens + max_new - 1) / max_new : n_seqs;
+    if (busy > n_seqs) busy = n_seqs;
+    if (busy < 1) busy = 1;
+    const long blocks = busy * H * ((P + SCAN_PTILE - 1) / SCAN_PTILE);
     long segs = 4L * PLM_SM_COUNT / blocks;               // four blocks an SM run at once: one wave of them
     const long most = max_new / 64;
     if (segs > most) segs = most;

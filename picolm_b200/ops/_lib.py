@@ -51,7 +51,7 @@ _SIGNATURES = {
     "plm_linear_scan": [_vp, _vp, _vp, _vp, _i, _l, _l, _l, _l, _i, _vp, _vp, _vp, _f, _f, _vp, _l, _vp, _l, _vp, _vp,
                         _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp],
     "plm_sigmoid_decay": [_vp, _i, _l, _vp, _f, _vp, _i, _i, _vp],
-    "plm_linear_scan_plan": [_i, _i, _i, _i, _i, _vp],
+    "plm_linear_scan_plan": [_i, _i, _i, _i, _i, _i, _vp],
     "plm_gated_norm": [_vp, _i, _l, _vp, _i, _l, _vp, _i, _vp, _i, _l, _i, _i, _i, _f, _i, _i, _i, _vp],
     "plm_head_linear": [_vp, _i, _l, _vp, _vp, _l, _vp, _l, _i, _i, _i, _i, _vp],
     "plm_store_rows_paged": [_vp, _i, _l, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],

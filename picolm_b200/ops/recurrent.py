@@ -97,7 +97,7 @@ def linear_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, raw: torch.Te
     y = torch.empty((T, H * P), dtype=torch.float32, device=v.device)
     # Long prompts are cut into segments that run side by side: a first pass leaves what each segment adds to the
     # state, a small kernel chains those into the state at every segment's start, a second pass gives y.
-    seg_len, n_segs = scan_plan(step.n_seqs, H, N, P, step.max_new)
+    seg_len, n_segs = scan_plan(step.n_seqs, H, N, P, step.max_new, T)
     seg_state = seg_decay = None
     kernels, run_mode = 1, mode
     if n_segs > 1:
@@ -125,15 +125,16 @@ def linear_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, raw: torch.Te
 _plans = {}
 
 
-def scan_plan(n_seqs: int, heads: int, key_dim: int, value_dim: int, max_new: int):
-    """(tokens per segment, segments of the longest sequence) of `linear_scan` for a step whose longest sequence brings
-    `max_new` tokens; one segment means one pass from the cache's state."""
-    key = (n_seqs, heads, key_dim, value_dim, max_new)
+def scan_plan(n_seqs: int, heads: int, key_dim: int, value_dim: int, max_new: int, n_tokens: int = 0):
+    """(tokens per segment, segments of the longest sequence) of `linear_scan` for a step of `n_tokens` tokens (0: not
+    known) whose longest sequence brings `max_new` of them; one segment means one pass from the cache's state."""
+    key = (n_seqs, heads, key_dim, value_dim, max_new, n_tokens)
     plan = _plans.get(key)
     if plan is None:
         import ctypes
         out = (ctypes.c_int * 2)()
-        _fn("recurrent", "plm_linear_scan_plan")(n_seqs, heads, key_dim, value_dim, int(max_new), ctypes.cast(out, ctypes.c_void_p))
+        _fn("recurrent", "plm_linear_scan_plan")(n_seqs, heads, key_dim, value_dim, int(max_new), int(n_tokens),
+                                                 ctypes.cast(out, ctypes.c_void_p))
         if len(_plans) > 4096:
             _plans.clear()
         plan = _plans[key] = (out[0], out[1])

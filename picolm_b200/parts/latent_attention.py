@@ -27,6 +27,7 @@ class LatentAttention(Part):
     uk [heads dim, kv_rank], uv [heads vdim, kv_rank], g [heads vdim, hidden], o [hidden, heads vdim]."""
 
     graph_safe = True
+    graph_safe_prompts = True       # padding tokens of a captured prompt step write the null page and are attended by nobody
 
     def __init__(self, params, runtime):
         super().__init__(params, runtime)

@@ -18,6 +18,10 @@ from .mixer import _stack_rows
 
 class _StateMixer(Part):
     graph_safe = True               # the step is read through device buffers only (seq_start, seq_slot, tok_seq)
+    # Captured prompt steps too: padding tokens belong to a sequence that `seq_start` gives no tokens, so the
+    # recurrence never visits them (their rows of y stay as they were allocated, and everything after works row by
+    # row); the convolution treats them as a sequence of the null slot; sequences without tokens leave their state.
+    graph_safe_prompts = True
 
     def _f32(self, t: torch.Tensor) -> torch.Tensor:
         return t.to(torch.float32).contiguous()

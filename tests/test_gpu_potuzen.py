@@ -494,6 +494,35 @@ def test_greedy_generation_through_the_entry_point(tmp_path):
     eng.cache.check()
 
 
+def test_bfloat16_generation_with_captured_prompt_steps(tmp_path):
+    """In bfloat16 `generate` replays captured graphs for the prompts' step too (tokens padded to a size class, the
+    padding in a sequence of its own): the logits of such a step equal those of the same prompts launched kernel by
+    kernel, states and caches are left the same (the tokens generated afterwards agree), and every generated token
+    is, by the exact logits, the best or within rounding of it."""
+    from picolm_b200.api import generate, model_load
+    d, tensors, config = _make(tmp_path, "pgraph", _config(MIXED, width=64, ff=128), seed=23, sharpen=1.0)
+    prompts = [random_tokens(n, 97, 60 + i) for i, n in enumerate([70, 9, 200])]
+    eng = model_load(d, dtype="bfloat16", max_batch=4)
+    assert eng.prompt_graphs, "every part of the design declares itself safe for captured prompt steps"
+    got = generate(eng, prompts, max_tokens=6, temperature=0.0, stop_ids=[])
+    assert eng._prompt_graphs, "the prompts' step was not replayed from a graph"
+    plain_eng = _engine(d, dtype="bfloat16", use_graphs=False)
+    slots = [plain_eng.new_sequence() for _ in prompts]
+    logits = plain_eng.step(list(zip(slots, prompts))).float().cpu()
+    seqs = [list(p) for p in prompts]
+    for step in range(6):
+        for i, row in enumerate(logits):
+            tok = got[i][step]
+            assert row[tok] >= row.max() - 0.02 * row.std(), f"request {i}, step {step}: graph and single launches disagree"
+            exact = _plain(tensors, config, seqs[i])[-1]
+            assert exact[tok] >= exact.max() - 0.25 * exact.std(), f"request {i}, step {step}: far from the exact best token"
+            seqs[i].append(tok)
+        logits = plain_eng.step([(s, [got[i][step]]) for i, s in enumerate(slots)]).float().cpu()
+    for s in slots:
+        plain_eng.end_sequence(s)
+    eng.cache.check()
+
+
 def test_trace_replay_as_a_user_runs_it(tmp_path):
     """bin/trace_run on a Potuzen folder: a batch of unequal prompts, single tokens until the shorter requests end,
     a request alone afterwards in the slot that was given back; more requests of a few tokens than the token count
