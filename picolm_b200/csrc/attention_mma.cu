@@ -265,7 +265,7 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, con
     }
     const int last_row = min(rows_total, row0 + 64) - 1;
     const int pos_min = pos0 + row0 / R, pos_max = pos0 + last_row / R;
-    const int first_key = (window > 0 && pos_min - window + 1 > 0) ? pos_min - window + 1 : 0;
+    const int first_key = plm_first_key(pos_min, window);
     const int page_first = first_key / PLM_PAGE, page_last = pos_max / PLM_PAGE;
     const int n_pages = page_last - page_first + 1;
 
@@ -282,8 +282,8 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, con
     const int r_lo = row0 + warp * 16 + (lane >> 2), r_hi = r_lo + 8;
     const int pos_lo = r_lo < rows_total ? pos0 + r_lo / R : -1;
     const int pos_hi = r_hi < rows_total ? pos0 + r_hi / R : -1;
-    const int lo_lo = (window > 0 && pos_lo - window + 1 > 0) ? pos_lo - window + 1 : 0;
-    const int lo_hi = (window > 0 && pos_hi - window + 1 > 0) ? pos_hi - window + 1 : 0;
+    const int lo_lo = plm_first_key(pos_lo, window);
+    const int lo_hi = plm_first_key(pos_hi, window);
 
     float o[HD / 8][4];
 #pragma unroll
@@ -421,7 +421,7 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, cons
     const int h0 = g * R + rg * 16;                     // first head of this row group
     const int n_rows = min(16, R - rg * 16);
     const int pos = PLM_POSITION(tok_pos[t]);
-    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int lo = plm_first_key(pos, window);
     const int page_first = lo / PLM_PAGE, page_last = pos / PLM_PAGE;
     const int total_pages = page_last - page_first + 1;
     const int per = (total_pages + n_splits - 1) / n_splits;

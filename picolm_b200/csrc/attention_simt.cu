@@ -6,7 +6,7 @@
 // with the running (max, sum, acc) update of the reference's `attn_core`
 // (picolm/model_attention.c:43-140; max starts at -1e30, causal by the loop
 // bound) taken 32 keys at a time.  lo = 0, or p - window + 1 for a sliding
-// window.  Keys and values of position t of sequence b live at
+// window, or the start of p's chunk for a mask of chunks (plm_first_key).  Keys and values of position t of sequence b live at
 //   cache[block_table[b][t / PLM_PAGE]][g][t % PLM_PAGE][0..hd)
 // and the new tokens' own K/V are already there when this kernel runs.
 //
@@ -45,7 +45,7 @@ attention_rows_kernel(const Ta* __restrict__ q, const Tc* __restrict__ kc, const
 #pragma unroll
     for (int i = 0; i < MAX_HD / 32; ++i) acc[i] = 0.f;
     float m = -1e30f, l = 0.f;
-    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int lo = plm_first_key(pos, window);
 
     for (int base = lo; base <= pos; base += 32) {
         const int key = base + lane;

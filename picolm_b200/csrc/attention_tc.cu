@@ -194,7 +194,7 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int rows = min(BQ, n_new - tile * BQ);
     const int g = h / (H / G);
     const int pos_last = pos0 + rows - 1;
-    const int first_key = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
+    const int first_key = plm_first_key(pos0, window);
     const int page_first = first_key / BKV, page_last = pos_last / BKV;
     const int n_pages = page_last - page_first + 1;
     const int* pages = block_table + (size_t)b * max_pages;
@@ -327,7 +327,7 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const int quarter = warp & 3;
         const int r = quarter * 32 + lane;                               // this thread's query row
         const int pos = r < rows ? pos0 + r : -1;                        // -1: no such row, everything masked
-        const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+        const int lo = plm_first_key(pos, window);
         const uint32_t lane_bits = (uint32_t)(quarter * 32) << 16;
         // O stays in tensor memory and the MMAs accumulate into it across pages.  Probabilities are
         // taken relative to a reference maximum m_ref that is raised (and O rescaled) only when a
@@ -340,7 +340,7 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             tc_fence_after();
             ATTN_TRACE(softmax_warp, i, 0);
             const int key0 = (page_first + i) * BKV;
-            const bool need_mask = key0 + BKV - 1 > pos0 || key0 < (window > 0 ? pos_last - window + 1 : 0);
+            const bool need_mask = key0 + BKV - 1 > pos0 || key0 < plm_first_key(pos_last, window);
             float mx = -INFINITY;
             uint32_t s0[32], s1[32];
             tc_ld32(tmem + lane_bits + TM_S + (i % NSB) * 64, s0);

@@ -42,6 +42,7 @@ LIBRARIES: Dict[str, List[str]] = {
     "attention_tc": ["attention_tc.cu"],            # likewise, head sizes 64 and 128
     "sampling": ["sampling.cu"],
     "recurrent": ["recurrent.cu"],
+    "routed": ["routed.cu"],
 }
 HEADERS = ["common.cuh", "tc_common.cuh", "gemm_tc_static.h"]
 

@@ -65,6 +65,16 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
     return red[32];
 }
 
+// The first key that a query at position `pos` sees (the last is `pos` itself).  `mask` > 0: a sliding window of
+// that many keys, the query's own included; `mask` < 0: chunks of -mask positions counted from position 0 of the
+// sequence (a query sees the keys of its own chunk up to itself); 0: every key.  Not decreasing in `pos`, so the
+// first key of a tile of queries is its first row's.  A row that does not exist (pos < 0) gets 0.
+__device__ __forceinline__ int plm_first_key(int pos, int mask) {
+    if (mask > 0) return pos - mask + 1 > 0 ? pos - mask + 1 : 0;
+    if (mask < 0 && pos > 0) return pos - pos % (-mask);
+    return 0;
+}
+
 // One rotary pair (picolm/tensor.c:3216-3304: x0' = x0 c - x1 s, x1' = x0 s + x1 c) with the roundings spelt
 // out (each product rounded, then the sum: what a plain implementation does), so that every kernel that
 // rotates gives the same bits whatever the compiler would fuse.

@@ -14,7 +14,7 @@
 // ------------------------------------------------------------------ embedding
 template <typename Tw>
 __global__ void embed_kernel(const int* __restrict__ tok, const Tw* __restrict__ table, float* __restrict__ out,
-                             int d, int vocab) {
+                             int d, int vocab, float scale) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
@@ -22,18 +22,21 @@ __global__ void embed_kernel(const int* __restrict__ tok, const Tw* __restrict__
     if (id < 0 || id >= vocab) id = 0;   // ids are checked on the host; never read outside the table
     const Tw* row = table + (size_t)id * d;
     float* o = out + (size_t)t * d;
-    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = to_f32<Tw>(row[i]);
+    // (a scale of 1 changes nothing: the product with 1.0f is exact)
+    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = __fmul_rn(to_f32<Tw>(row[i]), scale);
 }
 
+// out[t, :] = float(table[tok[t], :]) * scale (the reference has no scale; a design that multiplies its embeddings
+// by a constant gives it here)
 extern "C" int plm_embed(const int* tok, const void* table, int table_dtype, float* out, int n_tokens, int d,
-                         int vocab, cudaStream_t stream) {
+                         int vocab, float scale, cudaStream_t stream) {
     if (n_tokens <= 0) return PLM_OK;
     if (d <= 0 || vocab <= 0) return PLM_ERR_SHAPE;
     const int nt = d >= 1024 ? 256 : 128;
     if (table_dtype == PLM_F32)
-        return plm_status_of(launch_pdl(embed_kernel<float>, n_tokens, nt, 0, stream, tok, (const float*)table, out, d, vocab));
+        return plm_status_of(launch_pdl(embed_kernel<float>, n_tokens, nt, 0, stream, tok, (const float*)table, out, d, vocab, scale));
     if (table_dtype == PLM_BF16)
-        return plm_status_of(launch_pdl(embed_kernel<bf16>, n_tokens, nt, 0, stream, tok, (const bf16*)table, out, d, vocab));
+        return plm_status_of(launch_pdl(embed_kernel<bf16>, n_tokens, nt, 0, stream, tok, (const bf16*)table, out, d, vocab, scale));
     return PLM_ERR_DTYPE;
 }
 
@@ -276,9 +279,18 @@ template <> __device__ __forceinline__ float gate_act<0>(float g) { return g / (
 template <> __device__ __forceinline__ float gate_act<1>(float g) {
     return 0.5f * g * (1.0f + tanhf(0.79788456f * (g + 0.044715f * g * g * g)));
 }
+template <> __device__ __forceinline__ float gate_act<2>(float g) { return g; }       // (ACT 2 takes both branches: gate_clamped)
+
+// ACT 2: both branches clamped, a sigmoid gate with a slope, and the up branch shifted by one:
+//        g' = min(g, limit), u' = clamp(u, -limit, limit), out = g' sigmoid(slope g') (u' + 1)
+__device__ __forceinline__ float gate_clamped(float g, float u, float limit, float slope) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.0f + expf(-slope * g)) * (u + 1.0f);
+}
 
 template <typename T, int ACT>
-__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int F, size_t total) {
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int F, size_t total, float limit, float slope) {
     pdl_launch_dependents();
     pdl_wait();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -288,26 +300,30 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
         const int c = (int)(i - t * F);
         const float g = to_f32<T>(gu[t * 2 * F + c]);
         const float u = to_f32<T>(gu[t * 2 * F + F + c]);
-        out[i] = from_f32<T>(gate_act<ACT>(g) * u);
+        if constexpr (ACT == 2) out[i] = from_f32<T>(gate_clamped(g, u, limit, slope));
+        else out[i] = from_f32<T>(gate_act<ACT>(g) * u);
     }
 }
 
 template <typename T>
-static int launch_gated(int act, int blocks, cudaStream_t stream, const T* gu, T* out, int F, size_t total) {
-    if (act == 0) return plm_status_of(launch_pdl(swiglu_kernel<T, 0>, blocks, 256, 0, stream, gu, out, F, total));
-    if (act == 1) return plm_status_of(launch_pdl(swiglu_kernel<T, 1>, blocks, 256, 0, stream, gu, out, F, total));
+static int launch_gated(int act, int blocks, cudaStream_t stream, const T* gu, T* out, int F, size_t total, float limit,
+                        float slope) {
+    if (act == 0) return plm_status_of(launch_pdl(swiglu_kernel<T, 0>, blocks, 256, 0, stream, gu, out, F, total, 0.f, 0.f));
+    if (act == 1) return plm_status_of(launch_pdl(swiglu_kernel<T, 1>, blocks, 256, 0, stream, gu, out, F, total, 0.f, 0.f));
+    if (act == 2) return plm_status_of(launch_pdl(swiglu_kernel<T, 2>, blocks, 256, 0, stream, gu, out, F, total, limit, slope));
     return PLM_ERR_UNSUPPORTED;
 }
 
-// act: 0 silu, 1 gelu (tanh form)
-extern "C" int plm_swiglu(const void* gu, void* out, int dtype, int act, int n_rows, int F, cudaStream_t stream) {
+// act: 0 silu, 1 gelu (tanh form), 2 clamped branches with a sloped sigmoid gate (`limit`, `slope`)
+extern "C" int plm_swiglu(const void* gu, void* out, int dtype, int act, int n_rows, int F, float limit, float slope,
+                          cudaStream_t stream) {
     if (n_rows <= 0) return PLM_OK;
     if (F <= 0) return PLM_ERR_SHAPE;
     const size_t total = (size_t)n_rows * F;
     int blocks = (int)((total + 255) / 256);
     if (blocks > PLM_SM_COUNT * 16) blocks = PLM_SM_COUNT * 16;
-    if (dtype == PLM_F32) return launch_gated<float>(act, blocks, stream, (const float*)gu, (float*)out, F, total);
-    if (dtype == PLM_BF16) return launch_gated<bf16>(act, blocks, stream, (const bf16*)gu, (bf16*)out, F, total);
+    if (dtype == PLM_F32) return launch_gated<float>(act, blocks, stream, (const float*)gu, (float*)out, F, total, limit, slope);
+    if (dtype == PLM_BF16) return launch_gated<bf16>(act, blocks, stream, (const bf16*)gu, (bf16*)out, F, total, limit, slope);
     return PLM_ERR_DTYPE;
 }
 
@@ -495,4 +511,222 @@ extern "C" int plm_gather_rows(const void* src, void* dst, const int* rows, int 
     const int wide = row_bytes % 16 == 0 && src_ld_bytes % 16 == 0 && ((((uintptr_t)src | (uintptr_t)dst) & 15) == 0);
     return plm_status_of(launch_pdl(gather_rows_kernel, dim3(n_rows), dim3(256), 0, stream, (const uint8_t*)src,
                                     (uint8_t*)dst, rows, row_bytes, src_ld_bytes, wide));
+}
+
+// ------------------------------------------------------------------ layer norm
+// out = (v - mean) / sqrt(var + eps) * w with v = x (+ delta) (+ bias), mean and var (the mean squared deviation
+// from the mean) over the row, no bias after the weight.  One block per output row, like the RMSNorm above: row r
+// reads source row rows[r] (or r); with a delta or a bias the sum is written back to x unless rows are gathered.
+// `bias` [d] fp32 is a projection's bias that its product left out (a product's epilogue adds no bias).  The row
+// stays in shared memory between the passes (mean, deviations, output), so x is read once.
+template <typename Tw, typename To, int NT>
+__global__ void __launch_bounds__(NT)
+layernorm_kernel(float* __restrict__ x, const float* __restrict__ delta, const float* __restrict__ bias,
+                 const Tw* __restrict__ w, To* __restrict__ out, const int* __restrict__ rows, int d, float eps,
+                 int write_back) {
+    extern __shared__ float row_sm[];               // [d]
+    __shared__ float red[33];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int r = blockIdx.x;
+    const int src = rows ? PLM_ROW_NO(rows[r]) : r;
+    float* xr = x + (size_t)src * d;
+    const float* dr = delta ? delta + (size_t)src * d : nullptr;
+    float s = 0.f;
+    for (int i = threadIdx.x; i < d; i += NT) {
+        float v = xr[i];
+        if (dr) v += dr[i];
+        if (bias) v += bias[i];
+        if (write_back) xr[i] = v;
+        row_sm[i] = v;
+        s += v;
+    }
+    const float mean = block_sum<NT>(s, red) / (float)d;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < d; i += NT) {
+        const float c = row_sm[i] - mean;
+        ss += c * c;
+    }
+    ss = block_sum<NT>(ss, red);
+    const float scale = 1.0f / sqrtf(ss / (float)d + eps);
+    To* o = out + (size_t)r * d;
+    for (int i = threadIdx.x; i < d; i += NT) o[i] = from_f32<To>((row_sm[i] - mean) * scale * to_f32<Tw>(w[i]));
+}
+
+template <typename Tw, typename To>
+static int layernorm_launch(float* x, const float* delta, const float* bias, const void* w, void* out, const int* rows,
+                            int n_rows, int d, float eps, int write_back, cudaStream_t stream) {
+    // the block size (and with it the order of the sums) depends on the row's width only
+    const size_t smem = (size_t)d * sizeof(float);
+    if (d > 1024) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(layernorm_kernel<Tw, To, 1024>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        return plm_status_of(launch_pdl(layernorm_kernel<Tw, To, 1024>, n_rows, 1024, smem, stream, x, delta, bias,
+                                        (const Tw*)w, (To*)out, rows, d, eps, write_back));
+    }
+    return plm_status_of(launch_pdl(layernorm_kernel<Tw, To, 256>, n_rows, 256, smem, stream, x, delta, bias, (const Tw*)w,
+                                    (To*)out, rows, d, eps, write_back));
+}
+
+extern "C" int plm_layernorm(float* x, const float* delta, const float* bias, const void* w, int w_dtype, void* out,
+                             int out_dtype, const int* rows, int n_rows, int d, float eps, cudaStream_t stream) {
+    if (n_rows <= 0) return PLM_OK;
+    if (d <= 0 || d > 56 * 1024) return PLM_ERR_SHAPE;
+    const int write_back = ((delta != nullptr || bias != nullptr) && rows == nullptr) ? 1 : 0;
+    if (w_dtype == PLM_F32 && out_dtype == PLM_F32)
+        return layernorm_launch<float, float>(x, delta, bias, w, out, rows, n_rows, d, eps, write_back, stream);
+    if (w_dtype == PLM_BF16 && out_dtype == PLM_F32)
+        return layernorm_launch<bf16, float>(x, delta, bias, w, out, rows, n_rows, d, eps, write_back, stream);
+    if (w_dtype == PLM_F32 && out_dtype == PLM_BF16)
+        return layernorm_launch<float, bf16>(x, delta, bias, w, out, rows, n_rows, d, eps, write_back, stream);
+    if (w_dtype == PLM_BF16 && out_dtype == PLM_BF16)
+        return layernorm_launch<bf16, bf16>(x, delta, bias, w, out, rows, n_rows, d, eps, write_back, stream);
+    return PLM_ERR_DTYPE;
+}
+
+// x[t, :] += bias[:] in place on fp32 rows: a projection's bias, where nothing that follows can take it along.
+__global__ void add_bias_kernel(float* __restrict__ x, const float* __restrict__ bias, int d, size_t total) {
+    pdl_launch_dependents();
+    pdl_wait();
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < total; i += stride) x[i] += bias[i % d];
+}
+
+extern "C" int plm_add_bias(float* x, const float* bias, int n_rows, int d, cudaStream_t stream) {
+    if (n_rows <= 0) return PLM_OK;
+    if (d <= 0) return PLM_ERR_SHAPE;
+    const size_t total = (size_t)n_rows * d;
+    int blocks = (int)((total + 255) / 256);
+    if (blocks > PLM_SM_COUNT * 16) blocks = PLM_SM_COUNT * 16;
+    return plm_status_of(launch_pdl(add_bias_kernel, dim3(blocks), dim3(256), 0, stream, x, bias, d, total));
+}
+
+// ------------------------- bias + norm over the whole projection + RoPE + write into the cache
+// What stands between the QKV product and attention in a layer whose queries and keys are normalised over ALL
+// heads at once before they are rotated.  qkv is [T, nq + nk + nv] with nq = H * D query columns, then (a layer
+// that keeps keys and values of its own: own_kv) nk = G * D key columns and nv = G * Dv value columns; keys and
+// values may differ in width.  Per token, in fp32:
+//   q += bias_q; q *= 1 / sqrt(mean(q^2 over all nq columns) + eps) * wq;   the same for k with wk (null weights: no norm)
+//   the leading rot_dim components of every head of q and k are rotated by the token's position
+//   (pairing 0: (x[i], x[i + rot_dim/2]); pairing 1: (x[2i], x[2i+1])), the others pass
+//   v += bias_v
+// Queries go to q_out [T, H, hd_c], keys and values into the paged cache [pages, G, PLM_PAGE, hd_c]; hd_c >= D, Dv
+// is the one head size of the cache and of the attention kernels, and what lies beyond a head's own width is
+// written as zero (a zero component adds nothing to a score; a zero value column is multiplied by zero weights of
+// the output projection).  One block per token; the token's q and k sit in shared memory between the sums of
+// squares and the rotation; sums in an order that depends on the sizes only.
+template <typename Ta, typename Tw, typename Tc, int NT>
+__global__ void __launch_bounds__(NT)
+qk_norm_rope_store_kernel(const Ta* __restrict__ qkv, const float* __restrict__ bias, const Tw* __restrict__ wq,
+                          const Tw* __restrict__ wk, float eps, Tc* __restrict__ q_out, Tc* __restrict__ kc,
+                          Tc* __restrict__ vc, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                          const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
+                          const int* __restrict__ block_table, int max_pages, int H, int G, int D, int Dv, int hd_c,
+                          int rot_dim, int pairing, int own_kv) {
+    extern __shared__ float qk_sm[];                 // [nq + nk]
+    __shared__ float red[33];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int nq = H * D, nk = own_kv ? G * D : 0, nv = own_kv ? G * Dv : 0;
+    const int pos = PLM_POSITION(tok_pos[t]);
+    const Ta* row = qkv + (size_t)t * (nq + nk + nv);
+    float sq = 0.f, sk = 0.f;
+    for (int i = threadIdx.x; i < nq + nk; i += NT) {
+        float v = to_f32<Ta>(row[i]);
+        if (bias) v += bias[i];
+        qk_sm[i] = v;
+        if (i < nq) sq += v * v; else sk += v * v;
+    }
+    sq = block_sum<NT>(sq, red);
+    const float rq = wq ? 1.0f / sqrtf(sq / (float)nq + eps) : 1.0f;
+    float rk = 1.0f;
+    if (nk > 0) {
+        sk = block_sum<NT>(sk, red);
+        if (wk) rk = 1.0f / sqrtf(sk / (float)nk + eps);
+    }
+    size_t page_base = 0;
+    int in_page = 0;
+    bool have_page = false;
+    if (own_kv) {
+        const int page = PLM_PAGE_NO(block_table[(size_t)PLM_SEQ_NO(tok_seq[t]) * max_pages + pos / PLM_PAGE]);
+        have_page = page >= 0;
+        page_base = (size_t)(page < 0 ? 0 : page) * G;
+        in_page = pos % PLM_PAGE;
+    }
+    const int rot_half = rot_dim / 2, half_c = hd_c / 2;
+    const int heads = H + (own_kv ? G : 0);
+    // pairs of output components (ia, ib) of a head of hd_c: the rotated pairs first, then neighbours
+    for (int item = threadIdx.x; item < heads * half_c; item += NT) {
+        const int head = item / half_c, j = item - head * half_c;
+        int ia, ib;
+        const bool rotate = j < rot_half && cos_t != nullptr;
+        if (j < rot_half) {
+            if (pairing == 0) { ia = j; ib = j + rot_half; } else { ia = 2 * j; ib = 2 * j + 1; }
+        } else {
+            ia = rot_dim + 2 * (j - rot_half); ib = ia + 1;
+        }
+        const bool is_q = head < H;
+        const int hh = is_q ? head : head - H;
+        const float* src = qk_sm + (is_q ? 0 : nq) + hh * D;
+        const Tw* wn = is_q ? wq : wk;
+        const float r = is_q ? rq : rk;
+        float a = 0.f, b = 0.f;
+        if (ia < D) { a = src[ia]; if (wn) a = a * r * to_f32<Tw>(wn[hh * D + ia]); }
+        if (ib < D) { b = src[ib]; if (wn) b = b * r * to_f32<Tw>(wn[hh * D + ib]); }
+        if (rotate) {
+            const float c = cos_t[(size_t)pos * rot_half + j], s = sin_t[(size_t)pos * rot_half + j];
+            const float ra = rope_first(a, b, c, s), rb = rope_second(a, b, c, s);
+            a = ra; b = rb;
+        }
+        Tc* o;
+        if (is_q) {
+            o = q_out + ((size_t)t * H + hh) * hd_c;
+        } else {
+            if (!have_page) continue;
+            o = kc + ((page_base + hh) * PLM_PAGE + in_page) * hd_c;
+        }
+        o[ia] = from_f32<Tc>(a);
+        o[ib] = from_f32<Tc>(b);
+    }
+    if (own_kv && have_page) {
+        for (int item = threadIdx.x; item < G * hd_c; item += NT) {
+            const int g = item / hd_c, c = item - g * hd_c;
+            float v = 0.f;
+            if (c < Dv) {
+                v = to_f32<Ta>(row[nq + nk + g * Dv + c]);
+                if (bias) v += bias[nq + nk + g * Dv + c];
+            }
+            vc[((page_base + g) * PLM_PAGE + in_page) * hd_c + c] = from_f32<Tc>(v);
+        }
+    }
+}
+
+// qkv_dtype: the projection's result (PLM_F32, or PLM_BF16); out_dtype: queries, cache and norm weights.
+extern "C" int plm_qk_norm_rope_store(const void* qkv, int qkv_dtype, const float* bias, const void* wq, const void* wk,
+                                      float eps, void* q_out, void* kc, void* vc, int out_dtype, const float* cos_t,
+                                      const float* sin_t, const int* tok_pos, const int* tok_seq, const int* block_table,
+                                      int max_pages, int n_tokens, int H, int G, int D, int Dv, int hd_c, int rot_dim,
+                                      int pairing, int own_kv, cudaStream_t stream) {
+    if (n_tokens <= 0) return PLM_OK;
+    if (H <= 0 || G <= 0 || D <= 0 || Dv <= 0 || hd_c < D || hd_c < Dv || (hd_c & 1) || rot_dim < 0 || rot_dim > D ||
+        (rot_dim & 1))
+        return PLM_ERR_SHAPE;
+    if (pairing != 0 && pairing != 1) return PLM_ERR_UNSUPPORTED;
+    const size_t smem = (size_t)(H * D + (own_kv ? G * D : 0)) * sizeof(float);
+    if (smem > 200 * 1024) return PLM_ERR_SHAPE;
+#define QKN_LAUNCH(Ta_, Tc_)                                                                                           \
+    do {                                                                                                               \
+        if (smem > 48 * 1024)                                                                                          \
+            cudaFuncSetAttribute(qk_norm_rope_store_kernel<Ta_, Tc_, Tc_, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        return plm_status_of(launch_pdl(qk_norm_rope_store_kernel<Ta_, Tc_, Tc_, 256>, dim3(n_tokens), dim3(256), smem, stream, \
+                                        (const Ta_*)qkv, bias, (const Tc_*)wq, (const Tc_*)wk, eps, (Tc_*)q_out, (Tc_*)kc, \
+                                        (Tc_*)vc, cos_t, sin_t, tok_pos, tok_seq, block_table, max_pages, H, G, D, Dv,  \
+                                        hd_c, rot_dim, pairing, own_kv));                                              \
+    } while (0)
+    if (qkv_dtype == PLM_F32 && out_dtype == PLM_F32) QKN_LAUNCH(float, float);
+    if (qkv_dtype == PLM_F32 && out_dtype == PLM_BF16) QKN_LAUNCH(float, bf16);
+    if (qkv_dtype == PLM_BF16 && out_dtype == PLM_BF16) QKN_LAUNCH(bf16, bf16);
+#undef QKN_LAUNCH
+    return PLM_ERR_DTYPE;
 }

@@ -1,0 +1,368 @@
+// A routed feed-forward (mixture of experts): the router's choice, the sort of the chosen (token, expert) pairs by
+// expert, the experts' two products over those pairs, and the weighted sum per token.
+//
+//   scores   s_e = sigmoid(z_e) from the router's logits z (fp32); the choice is made on c_e = s_e + correction_e
+//   groups   the experts form n_groups equal groups of neighbours; a group's score is the sum of its two largest
+//            c_e; only experts of the `keep` best groups can be chosen (the others count as -inf)
+//   choice   the `top` largest c_e (the lower index on ties)
+//   weights  w = s_chosen / (sum of the chosen s + 1e-20) * scale     (s without the correction)
+//   expert   y = W_down (silu(W_gate h) * (W_up h)), no biases
+//   output   out[t] = sum_k w[t, k] y_(e[t, k])(h[t])  (+ gate[t] * shared[t] for an expert every token uses)
+//
+// Everything a later kernel needs of the choice stays on the device (nothing is read on the host, so the step can be
+// captured in a graph): the pairs ("entries", entry = token * top + k) are sorted into tiles of BM rows that belong to
+// one expert each (`moe_align`: sorted[tile * BM + r] = entry or -1, tile_expert[tile] = expert or -1), and the
+// products run over at most (entries + E * (BM - 1)) / BM tiles, a bound the host knows from the sizes alone.
+// A row of a product is the same sum in the same order wherever the row lands, so the result does not depend on what
+// else is in the batch.  All sums are fp32; the CUDA-core product serves the float32 run and shapes the tensor-core
+// product refuses.
+#include "common.cuh"
+
+namespace {
+
+constexpr int ROUTE_WARPS = 4;
+
+// ------------------------------------------------------------------- the choice
+// One warp per token.  logits [T, ld] fp32: columns [0, E) the router's, column `gate_col` (if gate != null) the
+// logit of a shared expert's gate.  ids [T, top] int32, weights [T, top] fp32, gate [T] fp32 = sigmoid(that logit).
+__global__ void __launch_bounds__(ROUTE_WARPS * 32)
+route_topk_kernel(const float* __restrict__ logits, int ld, const float* __restrict__ correction, int E, int top,
+                  int n_groups, int keep, float scale, int* __restrict__ ids, float* __restrict__ weights,
+                  float* __restrict__ gate, int gate_col, int T) {
+    extern __shared__ float route_sm[];             // per warp: s[E], c[E], group score[n_groups], group kept[n_groups]
+    pdl_launch_dependents();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * ROUTE_WARPS + warp;
+    if (t >= T) return;                             // warp-level exit; no block barrier below
+    float* s = route_sm + (size_t)warp * (2 * E + 2 * n_groups);
+    float* c = s + E;
+    float* gs = c + E;
+    float* kept = gs + n_groups;
+    const float* z = logits + (size_t)t * ld;
+    for (int e = lane; e < E; e += 32) {
+        const float v = 1.0f / (1.0f + expf(-z[e]));
+        float cv = v + (correction ? correction[e] : 0.f);
+        if (!(cv == cv)) cv = -INFINITY;            // a NaN is never chosen before anything else
+        s[e] = v;
+        c[e] = cv;
+    }
+    __syncwarp();
+    if (n_groups > 1 && keep < n_groups) {
+        const int per = E / n_groups;
+        for (int g = lane; g < n_groups; g += 32) {
+            float a = -INFINITY, b = -INFINITY;     // the two largest of the group
+            for (int j = 0; j < per; ++j) {
+                const float v = c[g * per + j];
+                if (v > a) { b = a; a = v; } else if (v > b) { b = v; }
+            }
+            gs[g] = per >= 2 ? a + b : a;
+            kept[g] = 0.f;
+        }
+        __syncwarp();
+        for (int r = 0; r < keep; ++r) {
+            float best = -INFINITY;
+            int bi = 0x7fffffff;
+            for (int g = lane; g < n_groups; g += 32) {
+                if (kept[g] != 0.f) continue;
+                float v = gs[g];
+                if (!(v == v)) v = -INFINITY;
+                if (v > best || (v == best && g < bi)) { best = v; bi = g; }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+            }
+            if (lane == 0 && bi < n_groups) kept[bi] = 1.f;
+            __syncwarp();
+        }
+        for (int e = lane; e < E; e += 32)
+            if (kept[e / per] == 0.f) c[e] = -INFINITY;
+        __syncwarp();
+    }
+    float sum = 0.f;
+    for (int r = 0; r < top; ++r) {
+        float best = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            const float v = c[e];
+            if (!(v == v)) continue;                // taken already
+            if (v > best || (v == best && e < bi)) { best = v; bi = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+        }
+        if (bi >= E) bi = 0;                        // more choices than experts: refused on the host
+        const float sv = s[bi];
+        sum += sv;
+        if (lane == 0) {
+            ids[(size_t)t * top + r] = bi;
+            weights[(size_t)t * top + r] = sv;
+            c[bi] = __int_as_float(0x7fc00000);     // NaN: taken
+        }
+        __syncwarp();
+    }
+    if (lane == 0) {
+        const float den = sum + 1e-20f;
+        for (int r = 0; r < top; ++r) weights[(size_t)t * top + r] = weights[(size_t)t * top + r] / den * scale;
+        if (gate) gate[t] = 1.0f / (1.0f + expf(-z[gate_col]));
+    }
+}
+
+// ---------------------------------------------------------------------- the sort
+// One block.  ids [n_entries] -> sorted [max_tiles * BM] (entry or -1), tile_expert [max_tiles] (expert or -1),
+// where [n_entries] the row of `sorted` that holds the entry.  Where an entry lands inside its expert's rows depends on
+// the order of the atomics; no result depends on it.
+constexpr int ALIGN_NT = 1024;
+__global__ void __launch_bounds__(ALIGN_NT)
+moe_align_kernel(const int* __restrict__ ids, int n_entries, int E, int BM, int* __restrict__ tile_expert,
+                 int* __restrict__ sorted, int* __restrict__ where, int max_tiles) {
+    extern __shared__ int align_sm[];               // cnt[E], off[E + 1], fill[E]
+    pdl_launch_dependents();
+    pdl_wait();
+    int* cnt = align_sm;
+    int* off = cnt + E;
+    int* fill = off + E + 1;
+    for (int e = threadIdx.x; e < E; e += ALIGN_NT) { cnt[e] = 0; fill[e] = 0; }
+    __syncthreads();
+    for (int i = threadIdx.x; i < n_entries; i += ALIGN_NT) {
+        int e = ids[i];
+        if (e < 0 || e >= E) e = 0;
+        atomicAdd(&cnt[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int o = 0;
+        for (int e = 0; e < E; ++e) {
+            off[e] = o;
+            o += (cnt[e] + BM - 1) / BM * BM;
+        }
+        off[E] = o;
+    }
+    __syncthreads();
+    for (int tile = threadIdx.x; tile < max_tiles; tile += ALIGN_NT) {
+        const int row = tile * BM;
+        int e = -1;
+        if (row < off[E]) {
+            int lo = 0, hi = E;                     // the last e with off[e] <= row
+            while (hi - lo > 1) {
+                const int mid = (lo + hi) >> 1;
+                if (off[mid] <= row) lo = mid; else hi = mid;
+            }
+            e = lo;
+        }
+        tile_expert[tile] = e;
+    }
+    for (int i = threadIdx.x; i < max_tiles * BM; i += ALIGN_NT) sorted[i] = -1;
+    __syncthreads();
+    for (int i = threadIdx.x; i < n_entries; i += ALIGN_NT) {
+        int e = ids[i];
+        if (e < 0 || e >= E) e = 0;
+        const int p = off[e] + atomicAdd(&fill[e], 1);
+        if (p < max_tiles * BM) sorted[p] = i;
+        where[i] = p;
+    }
+}
+
+// ------------------------------------------------------- the experts' products (CUDA cores)
+// A tile of BM sorted rows times a tile of 64 columns of its expert's weights, k ascending, fp32 sums.
+// MODE 0 (gate and up): row r of the tile is token sorted[...] / top of `a` [T, K]; w is [E][2 N][K], an expert's
+//   N gate rows followed by its N up rows; out[tile * BM + r, n] = silu(g) * u in To.
+// MODE 1 (down): row r of the tile is row tile * BM + r of `a` [max_tiles * BM, K]; w is [E][N][K];
+//   out[tile * BM + r, n] = sum in fp32 (the weighted sum per token comes after).
+constexpr int MG_BN = 64, MG_BK = 16;
+
+template <typename Ta, typename Tw, typename To, int BM, int MODE>
+__global__ void __launch_bounds__(256)
+moe_gemm_kernel(const Ta* __restrict__ a, long lda, int top, const Tw* __restrict__ w, To* __restrict__ out, long ldo,
+                const int* __restrict__ tile_expert, const int* __restrict__ sorted, int N, int K) {
+    constexpr int TM = BM / 16;
+    __shared__ float As[MG_BK][BM + 1];
+    __shared__ float Bs[MODE == 0 ? 2 : 1][MG_BK][MG_BN + 1];
+    __shared__ long a_off[BM];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int tile = blockIdx.x;
+    const int e = tile_expert[tile];
+    if (e < 0) return;
+    const int n0 = blockIdx.y * MG_BN;
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    for (int r = tid; r < BM; r += 256) {
+        const int entry = sorted[tile * BM + r];
+        a_off[r] = entry < 0 ? -1 : (MODE == 0 ? (long)(entry / top) * lda : (long)(tile * BM + r) * lda);
+    }
+    __syncthreads();
+    const Tw* wg = w + (size_t)e * (MODE == 0 ? 2 : 1) * N * K;
+    float acc[MODE == 0 ? 2 : 1][TM][4];
+#pragma unroll
+    for (int m = 0; m < (MODE == 0 ? 2 : 1); ++m)
+#pragma unroll
+        for (int i = 0; i < TM; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[m][i][j] = 0.f;
+    for (int k0 = 0; k0 < K; k0 += MG_BK) {
+        for (int idx = tid; idx < BM * MG_BK; idx += 256) {
+            const int r = idx / MG_BK, k = idx - r * MG_BK;
+            const long o = a_off[r];
+            As[k][r] = (o >= 0 && k0 + k < K) ? to_f32<Ta>(a[o + k0 + k]) : 0.f;
+        }
+        for (int idx = tid; idx < MG_BN * MG_BK; idx += 256) {
+            const int n = idx / MG_BK, k = idx - n * MG_BK;
+            const bool ok = n0 + n < N && k0 + k < K;
+            Bs[0][k][n] = ok ? to_f32<Tw>(wg[(size_t)(n0 + n) * K + k0 + k]) : 0.f;
+            if (MODE == 0) Bs[MODE == 0 ? 1 : 0][k][n] = ok ? to_f32<Tw>(wg[(size_t)(N + n0 + n) * K + k0 + k]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < MG_BK; ++k) {
+            float av[TM];
+#pragma unroll
+            for (int i = 0; i < TM; ++i) av[i] = As[k][ty * TM + i];
+#pragma unroll
+            for (int m = 0; m < (MODE == 0 ? 2 : 1); ++m)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float bv = Bs[m][k][tx * 4 + j];
+#pragma unroll
+                    for (int i = 0; i < TM; ++i) acc[m][i][j] = fmaf(av[i], bv, acc[m][i][j]);
+                }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < TM; ++i) {
+        const int r = ty * TM + i;
+        if (a_off[r] < 0) continue;
+        To* o = out + (size_t)(tile * BM + r) * ldo;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tx * 4 + j;
+            if (n >= N) continue;
+            if (MODE == 0) {
+                // both branches rounded to the activations' type first, as a product that stores them would
+                const float g = to_f32<To>(from_f32<To>(acc[0][i][j])), u = to_f32<To>(from_f32<To>(acc[MODE == 0 ? 1 : 0][i][j]));
+                o[n] = from_f32<To>(g / (1.0f + expf(-g)) * u);
+            } else {
+                o[n] = from_f32<To>(acc[0][i][j]);
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------ rows in sorted order
+// dst[p, :] = src[sorted[p] / top, :] (zero where sorted[p] < 0): the tokens' rows laid out as the sorted tiles want
+// them, for a product that takes whole tiles of its left operand.
+__global__ void moe_gather_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, const int* __restrict__ sorted,
+                                  int top, long row_bytes) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int p = blockIdx.x;
+    const int entry = sorted[p];
+    uint8_t* d = dst + (size_t)p * row_bytes;
+    if (entry < 0) {
+        for (long o = (long)threadIdx.x * 16; o < row_bytes; o += (long)blockDim.x * 16)
+            *reinterpret_cast<uint4*>(d + o) = make_uint4(0, 0, 0, 0);
+        return;
+    }
+    const uint8_t* s = src + (size_t)(entry / top) * row_bytes;
+    for (long o = (long)threadIdx.x * 16; o < row_bytes; o += (long)blockDim.x * 16)
+        *reinterpret_cast<uint4*>(d + o) = *reinterpret_cast<const uint4*>(s + o);
+}
+
+// ------------------------------------------------------------------- the weighted sum
+// out[t, :] = sum_k weights[t, k] * y[where[t * top + k], :]  (+ gate[t] * shared[t, :]), k ascending, fp32.
+__global__ void moe_combine_kernel(const float* __restrict__ y, long ldy, const int* __restrict__ where,
+                                   const float* __restrict__ weights, int top, const float* __restrict__ shared,
+                                   const float* __restrict__ gate, float* __restrict__ out, int d) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        float acc = 0.f;
+        for (int k = 0; k < top; ++k)
+            acc = fmaf(weights[(size_t)t * top + k], y[(size_t)where[(size_t)t * top + k] * ldy + i], acc);
+        if (shared) acc = fmaf(gate ? gate[t] : 1.0f, shared[(size_t)t * d + i], acc);
+        out[(size_t)t * d + i] = acc;
+    }
+}
+
+}  // namespace
+
+extern "C" int plm_route_topk(const float* logits, int ld, const float* correction, int E, int top, int n_groups,
+                              int keep, float scale, int* ids, float* weights, float* gate, int gate_col, int n_tokens,
+                              cudaStream_t stream) {
+    if (n_tokens <= 0) return PLM_OK;
+    if (E <= 0 || top <= 0 || top > E || n_groups <= 0 || E % n_groups || keep <= 0 || keep > n_groups || ld < E)
+        return PLM_ERR_SHAPE;
+    if (gate != nullptr && (gate_col < 0 || gate_col >= ld)) return PLM_ERR_SHAPE;
+    const size_t smem = (size_t)ROUTE_WARPS * (2 * E + 2 * n_groups) * sizeof(float);
+    if (smem > 200 * 1024) return PLM_ERR_SHAPE;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(route_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return plm_status_of(launch_pdl(route_topk_kernel, dim3((n_tokens + ROUTE_WARPS - 1) / ROUTE_WARPS), dim3(ROUTE_WARPS * 32),
+                                    smem, stream, logits, ld, correction, E, top, n_groups, keep, scale, ids, weights, gate,
+                                    gate_col, n_tokens));
+}
+
+// The most tiles of `bm` rows that `n_entries` pairs over `n_experts` experts can fill: every tile holds at least
+// one pair, and every expert leaves at most one tile part empty.
+extern "C" int plm_moe_max_tiles(int n_entries, int n_experts, int bm) {
+    const long a = ((long)n_entries + (long)n_experts * (bm - 1)) / bm;
+    return (int)(a < n_entries ? a : n_entries);
+}
+
+extern "C" int plm_moe_align(const int* ids, int n_entries, int E, int bm, int* tile_expert, int* sorted, int* where,
+                             int max_tiles, cudaStream_t stream) {
+    if (n_entries <= 0) return PLM_OK;
+    if (E <= 0 || bm <= 0 || max_tiles <= 0) return PLM_ERR_SHAPE;
+    const size_t smem = (size_t)(3 * E + 1) * sizeof(int);
+    if (smem > 200 * 1024) return PLM_ERR_SHAPE;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(moe_align_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return plm_status_of(launch_pdl(moe_align_kernel, dim3(1), dim3(ALIGN_NT), smem, stream, ids, n_entries, E, bm, tile_expert,
+                                    sorted, where, max_tiles));
+}
+
+// mode 0: gate/up with SiLU (a [T, K], out [max_tiles * bm, N] of a's type); mode 1: down (a [max_tiles * bm, K] of
+// `dtype`, out fp32).  bm 16 or 64.  dtype: a and w, PLM_F32 or PLM_BF16.
+extern "C" int plm_moe_gemm(const void* a, long lda, int top, const void* w, void* out, long ldo, int dtype, int mode,
+                            const int* tile_expert, const int* sorted, int max_tiles, int bm, int N, int K,
+                            cudaStream_t stream) {
+    if (max_tiles <= 0) return PLM_OK;
+    if (N <= 0 || K <= 0 || top <= 0) return PLM_ERR_SHAPE;
+    if (bm != 16 && bm != 64) return PLM_ERR_UNSUPPORTED;
+    const dim3 grid(max_tiles, (N + MG_BN - 1) / MG_BN), nt(256);
+#define MG_LAUNCH(Ta_, To_, BM_, MODE_)                                                                              \
+    return plm_status_of(launch_pdl(moe_gemm_kernel<Ta_, Ta_, To_, BM_, MODE_>, grid, nt, 0, stream, (const Ta_*)a, lda, top, \
+                                    (const Ta_*)w, (To_*)out, ldo, tile_expert, sorted, N, K))
+    if (dtype == PLM_F32) {
+        if (mode == 0) { if (bm == 16) MG_LAUNCH(float, float, 16, 0); else MG_LAUNCH(float, float, 64, 0); }
+        if (mode == 1) { if (bm == 16) MG_LAUNCH(float, float, 16, 1); else MG_LAUNCH(float, float, 64, 1); }
+    } else if (dtype == PLM_BF16) {
+        if (mode == 0) { if (bm == 16) MG_LAUNCH(bf16, bf16, 16, 0); else MG_LAUNCH(bf16, bf16, 64, 0); }
+        if (mode == 1) { if (bm == 16) MG_LAUNCH(bf16, float, 16, 1); else MG_LAUNCH(bf16, float, 64, 1); }
+    } else {
+        return PLM_ERR_DTYPE;
+    }
+#undef MG_LAUNCH
+    return PLM_ERR_UNSUPPORTED;
+}
+
+extern "C" int plm_moe_gather(const void* src, void* dst, const int* sorted, int n_rows, int top, long row_bytes,
+                              cudaStream_t stream) {
+    if (n_rows <= 0) return PLM_OK;
+    if (row_bytes <= 0 || row_bytes % 16 || (((uintptr_t)src | (uintptr_t)dst) & 15)) return PLM_ERR_ALIGN;
+    return plm_status_of(launch_pdl(moe_gather_kernel, dim3(n_rows), dim3(128), 0, stream, (const uint8_t*)src, (uint8_t*)dst,
+                                    sorted, top, row_bytes));
+}
+
+extern "C" int plm_moe_combine(const float* y, long ldy, const int* where, const float* weights, int top,
+                               const float* shared, const float* gate, float* out, int n_tokens, int d, cudaStream_t stream) {
+    if (n_tokens <= 0) return PLM_OK;
+    if (d <= 0 || top <= 0) return PLM_ERR_SHAPE;
+    return plm_status_of(launch_pdl(moe_combine_kernel, dim3(n_tokens), dim3(256), 0, stream, y, ldy, where, weights, top,
+                                    shared, gate, out, d));
+}

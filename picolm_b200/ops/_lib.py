@@ -17,10 +17,20 @@ _DT = {torch.float32: 0, torch.bfloat16: 1}
 _vp, _i, _l, _f = ctypes.c_void_p, ctypes.c_int, ctypes.c_long, ctypes.c_float
 
 _SIGNATURES = {
-    "plm_embed": [_vp, _vp, _i, _vp, _i, _i, _i, _vp],
+    "plm_embed": [_vp, _vp, _i, _vp, _i, _i, _i, _f, _vp],
     "plm_rmsnorm": [_vp, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _f, _vp],
     "plm_post_pre_norm": [_vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _f, _f, _vp],
-    "plm_swiglu": [_vp, _vp, _i, _i, _i, _i, _vp],
+    "plm_swiglu": [_vp, _vp, _i, _i, _i, _i, _f, _f, _vp],
+    "plm_layernorm": [_vp, _vp, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _f, _vp],
+    "plm_add_bias": [_vp, _vp, _i, _i, _vp],
+    "plm_qk_norm_rope_store": [_vp, _i, _vp, _vp, _vp, _f, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
+                               _i, _i, _i, _i, _vp],
+    "plm_route_topk": [_vp, _i, _vp, _i, _i, _i, _i, _f, _vp, _vp, _vp, _i, _i, _vp],
+    "plm_moe_max_tiles": [_i, _i, _i],
+    "plm_moe_align": [_vp, _i, _i, _i, _vp, _vp, _vp, _i, _vp],
+    "plm_moe_gemm": [_vp, _l, _i, _vp, _vp, _l, _i, _i, _vp, _vp, _i, _i, _i, _i, _vp],
+    "plm_moe_gather": [_vp, _vp, _vp, _i, _i, _l, _vp],
+    "plm_moe_combine": [_vp, _l, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _vp],
     "plm_rope_store": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
     "plm_gemm_tc_skinny": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _l, _l, _l, _vp, _vp],
     "plm_gemm_tc_skinny_residual": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _l, _l, _l, _l, _vp, _vp],

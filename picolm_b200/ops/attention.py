@@ -170,6 +170,14 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     return out
 
 
+class _MaskedView:
+    """A `KVLayerCache` seen through another mask: `window` holds the kernels' number (`key_mask`)."""
+    __slots__ = ("k", "v", "block_table", "window", "writable")
+
+    def __init__(self, kv, mask: int):
+        self.k, self.v, self.block_table, self.window, self.writable = kv.k, kv.v, kv.block_table, mask, kv.writable
+
+
 class Rotation:
     """A rotary encoding as the kernels take it: cos / sin tables [positions, rotary_dim / 2] in float32,
     how many leading components of a head are rotated, and how they pair up ("half" or "adjacent")."""
@@ -219,9 +227,23 @@ def attention_decode_rope(qkv: torch.Tensor, kv, step, num_heads: int, num_kv_he
     return out
 
 
-def attention(q: torch.Tensor, kv, step, num_kv_heads: int, scale: float) -> torch.Tensor:
+def key_mask(window: Optional[int], chunk: Optional[int] = None) -> int:
+    """The kernels' one number for which earlier keys a query sees: a sliding window of `window` keys (the query's
+    own included) as that number, chunks of `chunk` positions counted from position 0 of the sequence (a query sees
+    its own chunk up to itself) as its negative, 0 for every key."""
+    if window and chunk:
+        raise KernelError("attention: a sliding window and a mask of chunks at once are not supported")
+    if chunk is not None and chunk <= 0 or window is not None and window < 0:
+        raise KernelError("attention: a window or a chunk must be positive")
+    return -int(chunk) if chunk else int(window or 0)
+
+
+def attention(q: torch.Tensor, kv, step, num_kv_heads: int, scale: float, chunk: Optional[int] = None) -> torch.Tensor:
     """Causal attention of the step's queries over their sequences' cached keys
-    and values (`kv` is a `KVLayerCache`)."""
+    and values (`kv` is a `KVLayerCache`).  `chunk`: a mask of chunks of that many positions instead of the
+    cache's sliding window (see `key_mask`)."""
+    if chunk:
+        kv = _MaskedView(kv, key_mask(kv.window, chunk))
     if attention_mma_supported(q):
         if step.is_decode:
             splits = decode_splits(q.shape[0], q.shape[1], num_kv_heads, step.max_position + 1, q.shape[2])

@@ -8,15 +8,15 @@ import torch
 from ._lib import PAGE_TOKENS, KernelError, _check, _dev, _dt, _fn, _i32, _p, _stream, set_bounds
 
 
-def embed(tokens: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """out[t, :] = float(table[tokens[t], :]) as the fp32 residual stream."""
+def embed(tokens: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor] = None, scale: float = 1.0) -> torch.Tensor:
+    """out[t, :] = float(table[tokens[t], :]) * scale as the fp32 residual stream."""
     _i32(tokens, "tokens")
     _dev(table, "table")
     n, (vocab, d) = tokens.numel(), table.shape
     if out is None:
         out = torch.empty((n, d), dtype=torch.float32, device=table.device)
-    _check(_fn("elementwise", "plm_embed")(_p(tokens), _p(table), _dt(table, "table"), _p(out), n, d, vocab, _stream()),
-           "embed")
+    _check(_fn("elementwise", "plm_embed")(_p(tokens), _p(table), _dt(table, "table"), _p(out), n, d, vocab, float(scale),
+                                           _stream()), "embed")
     return out
 
 
@@ -97,10 +97,13 @@ def gather_rows(x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
     return out
 
 
-GATE_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+# "swish_clamped": g' = min(g, limit), u' = clamp(u, -limit, limit), g' sigmoid(slope g') (u' + 1); its two constants
+# are arguments of `swiglu`
+GATE_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "swish_clamped": 2}
 
 
-def swiglu(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None, activation: str = "silu") -> torch.Tensor:
+def swiglu(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None, activation: str = "silu", limit: float = 0.0,
+           slope: float = 1.0) -> torch.Tensor:
     """gate_up [T, 2F] (gate columns first) -> act(gate) * up, [T, F]; `activation` "silu" or "gelu_tanh"
     (the reference's two: picolm/tensor.c:3306-3323)."""
     _dev(gate_up, "gate_up")
@@ -112,7 +115,8 @@ def swiglu(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None, activation
     if out is None:
         out = torch.empty((T, F2 // 2), dtype=gate_up.dtype, device=gate_up.device)
     _check(_fn("elementwise", "plm_swiglu")(_p(gate_up), _p(out), _dt(gate_up, "gate_up"),
-                                            GATE_ACTIVATIONS[activation], T, F2 // 2, _stream()), "swiglu")
+                                            GATE_ACTIVATIONS[activation], T, F2 // 2, float(limit), float(slope),
+                                            _stream()), "swiglu")
     return out
 
 
@@ -148,3 +152,98 @@ def rope_store(qkv: torch.Tensor, q_out: torch.Tensor, k_cache: Optional[torch.T
         _p(qkv), _p(q_out), _p(k_cache) if store else None, _p(v_cache) if store else None, _dt(qkv, "qkv"),
         _p(cos), _p(sin), _p(tok_pos), _p(tok_seq), _p(block_table), block_table.shape[1], T, H, G, hd,
         rotary_dim, 0 if pairing == "half" else 1, 1 if store else 0, _stream()), "rope_store")
+
+
+def layernorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.dtype,
+              delta: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
+              rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Layer norm with a weight and no bias of the fp32 stream `x` [T, d]: `(v - mean) / sqrt(var + eps) * w`.  With
+    `delta` (fp32 [T, d], or a product that has not run) and / or `bias` (fp32 [d], a projection's bias that its product
+    left out) v = x + delta + bias, written back to x unless `rows` gathers.  `rows` (int32) picks the source rows."""
+    _dev(x, "x"), _dev(weight, "weight")
+    if x.dtype != torch.float32:
+        raise KernelError("the residual stream must be float32")
+    T, d = x.shape
+    if weight.shape != (d,):
+        raise KernelError(f"norm weight has shape {tuple(weight.shape)}, the stream is {d} wide")
+    if hasattr(delta, "compute"):                          # a product that has not run yet (gemm.PendingLinear)
+        if rows is None and delta.adds_in_place(x):        # many rows: the add in the product's epilogue
+            delta.add_into(x)
+            delta = None
+        else:
+            delta = delta.compute()
+    if delta is not None:
+        _dev(delta, "delta")
+        if delta.dtype != torch.float32 or delta.shape != x.shape:
+            raise KernelError("delta must be float32 and shaped like x")
+    if bias is not None:
+        _dev(bias, "bias")
+        if bias.dtype != torch.float32 or bias.shape != (d,):
+            raise KernelError("bias must be float32 [d]")
+    n_rows = T
+    if rows is not None:
+        _i32(rows, "rows")
+        n_rows = rows.numel()
+    out = torch.empty((n_rows, d), dtype=out_dtype, device=x.device)
+    set_bounds("elementwise", n_rows=T, device=x.device)
+    _check(_fn("elementwise", "plm_layernorm")(
+        _p(x), _p(delta), _p(bias), _p(weight), _dt(weight, "weight"), _p(out), _dt(out, "out"), _p(rows), n_rows, d,
+        float(eps), _stream()), f"layernorm rows={n_rows} d={d}",
+        nbytes=n_rows * d * (4 + (8 if delta is not None or bias is not None else 0) + out.element_size()))
+    return out
+
+
+def add_bias(x: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+    """x [T, d] += bias [d] in place, both float32; returns x."""
+    _dev(x, "x"), _dev(bias, "bias")
+    if x.dtype != torch.float32 or bias.dtype != torch.float32 or x.dim() != 2 or bias.shape != (x.shape[1],):
+        raise KernelError("add_bias takes float32 rows [T, d] and a float32 bias [d]")
+    _check(_fn("elementwise", "plm_add_bias")(_p(x), _p(bias), x.shape[0], x.shape[1], _stream()), "add_bias",
+           nbytes=2 * x.numel() * 4)
+    return x
+
+
+def qk_norm_rope_store(qkv: torch.Tensor, bias: Optional[torch.Tensor], q_norm: Optional[torch.Tensor],
+                       k_norm: Optional[torch.Tensor], eps: float, q_out: torch.Tensor, kv, rotation, step,
+                       num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int, own_kv: bool = True) -> None:
+    """What stands between a QKV product and attention where queries and keys are normalised over all their heads at
+    once: per token, in fp32, `q + bias` and `k + bias` are divided by their root mean square over ALL their columns
+    and multiplied by `q_norm` / `k_norm` (None: no norm), the leading `rotation.rotary_dim` components of every head
+    are rotated by the token's position, `v + bias` passes.  `qkv` [T, H*D (+ G*D + G*Dv)] float32 or the run's type;
+    queries go to `q_out` [T, H, hd_c], keys and values (`own_kv`) into the pages of `kv` (a `KVLayerCache` whose
+    head size hd_c >= D, Dv: what lies beyond a head's own width is written as zero).  `rotation`: `ops.Rotation` or
+    None."""
+    _dev(qkv, "qkv"), _dev(q_out, "q_out")
+    _i32(step.tok_pos, "tok_pos"), _i32(step.tok_seq, "tok_seq"), _i32(kv.block_table, "block_table")
+    T = qkv.shape[0]
+    H, G, D, Dv = num_heads, num_kv_heads, key_dim, value_dim
+    hd_c = q_out.shape[2]
+    cols = H * D + ((G * D + G * Dv) if own_kv else 0)
+    if qkv.shape != (T, cols) or q_out.shape != (T, H, hd_c):
+        raise KernelError("qk_norm_rope_store: qkv / q_out shapes do not match the head counts")
+    if own_kv:
+        for c, n in ((kv.k, "k_cache"), (kv.v, "v_cache")):
+            _dev(c, n)
+            if c.dtype != q_out.dtype or c.shape[1:] != (G, PAGE_TOKENS, hd_c):
+                raise KernelError(f"qk_norm_rope_store: {n} must be [pages, {G}, {PAGE_TOKENS}, {hd_c}] of {q_out.dtype}")
+    if bias is not None and (bias.dtype != torch.float32 or bias.shape != (cols,) or not bias.is_cuda):
+        raise KernelError("qk_norm_rope_store: bias must be float32, one per column of qkv")
+    for wn, n, size in ((q_norm, "q_norm", H * D), (k_norm if own_kv else None, "k_norm", G * D)):
+        if wn is not None and (wn.dtype != q_out.dtype or wn.shape != (size,) or not wn.is_cuda):
+            raise KernelError(f"qk_norm_rope_store: {n} must be [{size}] of {q_out.dtype}")
+    cos = sin = None
+    rot, pairing = 0, "half"
+    if rotation is not None and rotation.cos is not None:
+        cos, sin, rot, pairing = rotation.cos, rotation.sin, rotation.rotary_dim, rotation.pairing
+        if cos.dtype != torch.float32 or cos.shape[1] != rot // 2 or sin.shape != cos.shape:
+            raise KernelError("qk_norm_rope_store: cos/sin tables must be float32 [positions, rotary_dim/2]")
+        if step.max_position >= cos.shape[0]:
+            raise KernelError(f"position {step.max_position} lies beyond the rotary table")
+    set_bounds("elementwise", n_pages=kv.k.shape[0] if own_kv else 0, n_seqs=kv.block_table.shape[0],
+               n_positions=kv.block_table.shape[1] * PAGE_TOKENS, device=qkv.device)
+    _check(_fn("elementwise", "plm_qk_norm_rope_store")(
+        _p(qkv), _dt(qkv, "qkv"), _p(bias), _p(q_norm), _p(k_norm) if own_kv else None, float(eps), _p(q_out),
+        _p(kv.k) if own_kv else None, _p(kv.v) if own_kv else None, _dt(q_out, "q_out"), _p(cos), _p(sin),
+        _p(step.tok_pos), _p(step.tok_seq), _p(kv.block_table), kv.block_table.shape[1], T, H, G, D, Dv, hd_c, rot,
+        0 if pairing == "half" else 1, 1 if own_kv else 0, _stream()), f"qk_norm_rope_store T={T}",
+        nbytes=qkv.numel() * qkv.element_size() + T * (H + (2 * G if own_kv else 0)) * hd_c * q_out.element_size())

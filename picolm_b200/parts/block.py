@@ -70,7 +70,9 @@ class Arrangement(Part):
 
 @register_part("arrangement", "pre_norm")
 class PreNormBlock(Arrangement):
-    wants = ("mixer_norm", "mixer", "feed_forward_norm", "feed_forward")
+    """`x += mixer(norm(x)); x += feed_forward(norm'(x))`; the feed-forward and its norm are optional (a layer that
+    only mixes)."""
+    wants = ("mixer_norm", "mixer")
 
     narrows_rows = True
 
@@ -85,17 +87,19 @@ class PreNormBlock(Arrangement):
                 stream.pending = None
                 return
             stream.narrow(keep_rows)
+        if "feed_forward" not in self.named:
+            return
         h = self._norm(self.feed_forward_norm, self.feed_forward, stream)
         stream.pending = self.feed_forward.forward(h, step)
 
 
 def pre_norm_layer(prefix: str, mixer: PartSpec, feed_forward: PartSpec, mixer_norm: PartSpec,
                    feed_forward_norm: PartSpec, cache_of=None) -> LayerSpec:
-    """The spec of a `pre_norm` layer from its four parts."""
-    return LayerSpec(prefix, "pre_norm", {
-        "mixer_norm": ("norm", mixer_norm), "mixer": ("mixer", mixer),
-        "feed_forward_norm": ("norm", feed_forward_norm), "feed_forward": ("feed_forward", feed_forward),
-    }, cache_of=cache_of)
+    """The spec of a `pre_norm` layer from its four parts; without `feed_forward` the layer only mixes."""
+    parts = {"mixer_norm": ("norm", mixer_norm), "mixer": ("mixer", mixer)}
+    if feed_forward is not None:
+        parts.update({"feed_forward_norm": ("norm", feed_forward_norm), "feed_forward": ("feed_forward", feed_forward)})
+    return LayerSpec(prefix, "pre_norm", parts, cache_of=cache_of)
 
 
 @register_part("arrangement", "sandwich_norm")

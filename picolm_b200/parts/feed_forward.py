@@ -17,7 +17,8 @@ from .mixer import _stack_rows
 @register_part("feed_forward", "gated_mlp")
 class GatedMLP(Part):
     """params: hidden_size, intermediate_size, activation ("silu", or "gelu_tanh": the reference's gelu,
-    picolm/tensor.c:3317-3323), gate_name/up_name/down_name (relative tensor names).  The product whose
+    picolm/tensor.c:3317-3323; or "swish_clamped" with its constants `limit` and `slope`: g' = min(g, limit),
+    u' = clamp(u, -limit, limit), g' sigmoid(slope g') (u' + 1)), gate_name/up_name/down_name (relative tensor names).  The product whose
     epilogue applies the activation exists for both (a build variant of the kernels for gelu_tanh); operands the
     tensor cores do not take run a plain product and the activation as a kernel of its own."""
 
@@ -59,5 +60,107 @@ class GatedMLP(Part):
             # handed to the next product and nowhere else
             act = ops.linear_swiglu(h, self.w_gate_up, defer=True, activation=self.params["activation"])
         else:
-            act = ops.swiglu(ops.linear(h, self.w_gate_up, self.runtime.dtype), activation=self.params["activation"])
+            act = ops.swiglu(ops.linear(h, self.w_gate_up, self.runtime.dtype), activation=self.params["activation"],
+                             limit=float(self.params.get("limit", 0.0)), slope=float(self.params.get("slope", 1.0)))
         return ops.linear(act, self.w_down, torch.float32, defer=True)
+
+
+@register_part("feed_forward", "routed_mlp")
+class RoutedMLP(Part):
+    """A mixture of experts: every token uses `top` of `experts` small gated MLPs (`W_down(silu(W_gate h) * W_up h)`,
+    no biases), chosen by a router, and optionally one shared expert that every token uses.
+
+    params: hidden_size, experts, top, expert_size (an expert's inner width), route_scale, groups (None, or
+    {"count", "keep"}: the experts form `count` equal groups of neighbours, and only experts of the `keep` groups with
+    the largest sums of their two best choice scores can be chosen), correction_name (None, or a tensor [experts]
+    added to the scores for the choice only), router_name, expert_prefix (expert e's tensors are
+    `<expert_prefix><e>.<gate_name|up_name|down_name>`), gate_name/up_name/down_name, shared (None, or
+    {"size", "prefix", "gate"}: the shared expert's inner width, its tensors' prefix, and the name under that prefix of
+    the [1, hidden] row whose sigmoid multiplies the shared expert's result per token; None: no such gate).
+
+    The router's logits are a float32 product; scores are `sigmoid(logit)`; the weights of the chosen experts are
+    their scores (without the correction) divided by their sum (+ 1e-20), times `route_scale`.  The choice stays on
+    the device: the chosen (token, expert) pairs are sorted by expert into tiles, and the experts' products run over
+    those tiles (`ops/routed.py`)."""
+
+    graph_safe = True
+    graph_safe_prompts = True
+
+    def __init__(self, params, runtime):
+        super().__init__(params, runtime)
+        p = self.params
+        self.E, self.top, self.F, self.d = int(p["experts"]), int(p["top"]), int(p["expert_size"]), int(p["hidden_size"])
+        g = p.get("groups")
+        self.n_groups, self.keep = (int(g["count"]), int(g["keep"])) if g else (1, 1)
+        if not 0 < self.top <= self.E or self.E % self.n_groups or not 0 < self.keep <= self.n_groups:
+            raise ValueError(f"routed_mlp: top={self.top}, experts={self.E}, groups={self.n_groups}, kept={self.keep} "
+                             f"do not fit together")
+        if self.top > self.keep * (self.E // self.n_groups):
+            raise ValueError(f"routed_mlp: {self.keep} groups of {self.E // self.n_groups} experts cannot give {self.top} choices")
+        self.shared = None
+        sh = p.get("shared")
+        if sh:
+            self.shared = GatedMLP({"hidden_size": self.d, "intermediate_size": int(sh["size"]), "activation": "silu",
+                                    "gate_name": p["gate_name"], "up_name": p["up_name"], "down_name": p["down_name"]}, runtime)
+
+    def _expert(self, e: int, which: str) -> str:
+        return f"{self.params['expert_prefix']}{e}.{self.params[which]}"
+
+    def weight_specs(self):
+        p = self.params
+        specs = {p["router_name"]: WeightSpec((self.E, self.d))}
+        if p.get("correction_name"):
+            specs[p["correction_name"]] = WeightSpec((self.E,), init="normal")
+        for e in range(self.E):
+            specs[self._expert(e, "gate_name")] = WeightSpec((self.F, self.d))
+            specs[self._expert(e, "up_name")] = WeightSpec((self.F, self.d))
+            specs[self._expert(e, "down_name")] = WeightSpec((self.d, self.F))
+        if self.shared is not None:
+            sh = p["shared"]
+            for rel, ws in self.shared.weight_specs().items():
+                specs[f"{sh['prefix']}.{rel}"] = ws
+            if sh.get("gate"):
+                specs[f"{sh['prefix']}.{sh['gate']}"] = WeightSpec((1, self.d))
+        return specs
+
+    def load(self, tensors):
+        p = self.params
+        rows = [tensors[p["router_name"]]]
+        self.gate_col = None
+        if self.shared is not None:
+            sh = p["shared"]
+            self.shared.load({rel: tensors[f"{sh['prefix']}.{rel}"] for rel in self.shared.weight_specs()})
+            if sh.get("gate"):
+                rows.append(tensors[f"{sh['prefix']}.{sh['gate']}"])
+                self.gate_col = self.E
+        # the router and the shared expert's gate as one float32 product: [experts (+ 1), hidden]
+        self.w_router = _stack_rows(rows)
+        self.correction = (tensors[p["correction_name"]].to(torch.float32).contiguous() if p.get("correction_name") else None)
+        # [E, 2F, d]: an expert's gate rows, then its up rows; [E, d, F]
+        self.w_gate_up = torch.stack([torch.cat([tensors[self._expert(e, "gate_name")], tensors[self._expert(e, "up_name")]])
+                                      for e in range(self.E)]).contiguous()
+        self.w_down = torch.stack([tensors[self._expert(e, "down_name")] for e in range(self.E)]).contiguous()
+
+    def weight_bytes(self):
+        """What a decode step of one token reads: the router, `top` experts, the shared expert."""
+        per = (self.w_gate_up.numel() + self.w_down.numel()) // self.E * self.w_down.element_size()
+        return (self.w_router.numel() * self.w_router.element_size() + self.top * per
+                + (self.shared.weight_bytes() if self.shared is not None else 0))
+
+    def forward(self, h, step):
+        if hasattr(h, "materialize"):
+            h = h.materialize()
+        T = h.shape[0]
+        logits = ops.gemm_simt(h, self.w_router, torch.float32)
+        ids, weights, gate = ops.route_topk(logits, self.E, self.top, self.correction, self.n_groups, self.keep,
+                                            float(self.params["route_scale"]), self.gate_col)
+        # few pairs an expert (decode steps): small tiles, so that a tile's padding costs little
+        bm = 16 if T * self.top <= 16 * self.E else 64
+        pairs = ops.moe_align(ids, self.E, bm)
+        act = ops.moe_gate_up(h, self.w_gate_up, pairs)
+        y = ops.moe_down(act, self.w_down, pairs)
+        shared = None
+        if self.shared is not None:
+            shared = self.shared.forward(h, step)
+            shared = shared.compute() if hasattr(shared, "compute") else shared
+        return ops.moe_combine(y, pairs, weights, shared, gate)

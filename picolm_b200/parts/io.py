@@ -14,7 +14,8 @@ from .base import Part, WeightSpec, register_part
 
 @register_part("embedding", "token_embedding")
 class TokenEmbedding(Part):
-    """params: vocab_size, hidden_size, name (absolute tensor name)."""
+    """params: vocab_size, hidden_size, name (absolute tensor name), scale (optional: the rows are multiplied by it
+    in float32 as they enter the stream; the reference has none)."""
 
     def weight_specs(self):
         return {self.params["name"]: WeightSpec((self.params["vocab_size"], self.params["hidden_size"]))}
@@ -23,7 +24,7 @@ class TokenEmbedding(Part):
         self.table = tensors[self.params["name"]]
 
     def forward(self, step):
-        return ops.embed(step.tok_ids, self.table)
+        return ops.embed(step.tok_ids, self.table, scale=float(self.params.get("scale", 1.0)))
 
 
 @register_part("head", "lm_head")

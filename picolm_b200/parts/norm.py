@@ -10,7 +10,7 @@ import torch
 
 from .. import ops
 from .base import Part, WeightSpec, register_part
-from .stream import PostNormed, ResidualStream
+from .stream import BiasedDelta, PostNormed, ResidualStream
 
 
 @register_part("norm", "rmsnorm")
@@ -51,6 +51,8 @@ class RMSNorm(Part):
                 return ops.post_pre_norm(stream.x, p.delta, p.norm.weight, p.norm.params["eps"], self.weight,
                                          self.params["eps"], self.runtime.dtype)
             stream.pending = p.compute()
+        if isinstance(stream.pending, BiasedDelta):
+            stream.pending = stream.pending.compute()
         if (defer_scale and rows is None
                 and ops.residual_norm_supported(stream.pending, stream.x, self.weight)):
             h = ops.linear_residual_norm(stream.pending, stream.x, self.weight, self.params["eps"])
@@ -66,3 +68,40 @@ class RMSNorm(Part):
         """The norm of float32 rows that are not the stream (a sublayer's result, normalised before it is added);
         float32 [T, size]."""
         return ops.rmsnorm(rows, self.weight, self.params["eps"], torch.float32)
+
+
+@register_part("norm", "layernorm")
+class LayerNorm(Part):
+    """Layer norm with a weight and no bias: `(x - mean) / sqrt(var + eps) * w`, var the mean squared deviation.
+    params: size, eps, name (the weight's tensor name relative to the part's prefix; default "weight", "" for a
+    tensor that is called by the prefix alone).  Weight: [size].  Statistics and the stream in float32."""
+
+    graph_safe = True
+    graph_safe_prompts = True
+
+    @property
+    def _name(self) -> str:
+        return self.params.get("name", "weight")
+
+    def weight_specs(self):
+        return {self._name: WeightSpec((self.params["size"],), init="ones_normal")}
+
+    def load(self, tensors):
+        self.weight = tensors[self._name]
+
+    def weight_bytes(self):
+        return self.weight.numel() * self.weight.element_size()
+
+    def forward(self, stream: ResidualStream, rows: Optional[torch.Tensor] = None, defer_scale: bool = False):
+        """Normalise `x + pending` (the pending delta with its bias, if it has one, added in the same pass).  Without
+        `rows` the sum is written back to the stream and the delta is consumed; with `rows` only those rows are
+        normalised and the stream is left as it is."""
+        p, bias = stream.pending, None
+        if isinstance(p, PostNormed):
+            p = p.compute()
+        if isinstance(p, BiasedDelta):
+            p, bias = p.delta, p.bias
+        h = ops.layernorm(stream.x, self.weight, self.params["eps"], self.runtime.dtype, delta=p, bias=bias, rows=rows)
+        if rows is None:
+            stream.pending = None
+        return h

@@ -28,6 +28,28 @@ class PostNormed:
         return False
 
 
+class BiasedDelta:
+    """A sublayer's result whose last projection has a bias that no product's epilogue adds: `delta` (float32 rows,
+    or a product that has not run) plus `bias` (float32 [d]).  A norm that reads the stream next may add both in its
+    own pass; anything else calls `compute()`."""
+    __slots__ = ("delta", "bias")
+
+    def __init__(self, delta, bias: torch.Tensor):
+        self.delta, self.bias = delta, bias
+
+    @property
+    def shape(self):
+        return self.delta.shape
+
+    def compute(self) -> torch.Tensor:
+        from .. import ops
+        rows = self.delta.compute() if hasattr(self.delta, "compute") else self.delta
+        return ops.add_bias(rows, self.bias)
+
+    def adds_in_place(self, x: torch.Tensor) -> bool:
+        return False
+
+
 @dataclass
 class ResidualStream:
     x: torch.Tensor                              # fp32 [T, d]
@@ -40,13 +62,19 @@ class ResidualStream:
         (`ops.PendingLinear`) is narrowed at its left operand: it then runs on those rows."""
         from .. import ops
         self.x = ops.gather_rows(self.x, rows)
-        p = self.pending
-        if p is not None:
-            if isinstance(p, PostNormed):
-                self.pending = PostNormed(ops.gather_rows(p.delta, rows), p.norm)
-            elif isinstance(p, ops.PendingLinear):
-                a = p.a.materialize() if isinstance(p.a, ops.LazyRows) else p.a
-                self.pending = ops.PendingLinear(ops.gather_rows(a, rows), p.w)
-            else:
-                self.pending = ops.gather_rows(p, rows)
+        if self.pending is not None:
+            self.pending = _narrowed(self.pending, rows)
         self.narrowed = True
+
+
+def _narrowed(p, rows):
+    """The pending delta `p` at the rows `rows` only."""
+    from .. import ops
+    if isinstance(p, PostNormed):
+        return PostNormed(ops.gather_rows(p.delta, rows), p.norm)
+    if isinstance(p, BiasedDelta):
+        return BiasedDelta(_narrowed(p.delta, rows), p.bias)
+    if isinstance(p, ops.PendingLinear):
+        a = p.a.materialize() if isinstance(p.a, ops.LazyRows) else p.a
+        return ops.PendingLinear(ops.gather_rows(a, rows), p.w)
+    return ops.gather_rows(p, rows)
