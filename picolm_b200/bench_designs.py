@@ -1,7 +1,7 @@
-"""Throughput of a hybrid design beside the Llama decoder at equal layer sizes (random weights): prefill
+"""Throughput of another design (Potuzen, Kunulorn) beside the Llama decoder at equal layer sizes (random weights): prefill
 tokens/s of one prompt and decode tokens/s of a batch, at a few sizes that resemble a real model's layers,
 and, with `kernels=True`, the device time of every kind of launch with the fraction of the memory's or the
-tensor cores' measured rate that it reaches.  `bench.py --design potuzen` calls this."""
+tensor cores' measured rate that it reaches.  `bench.py --design potuzen|kunulorn` calls this."""
 from __future__ import annotations
 
 import json
@@ -30,6 +30,28 @@ def potuzen_config(width: int, ff: int, layers: int, vocab: int) -> dict:
     mlp = {"kind": "dense", "ff": ff}
     return {"architecture": "Potuzen", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
             "layers": [dict(turn[i % 4], mlp=mlp) for i in range(layers)]}
+
+
+def kunulorn_config(width: int, ff: int, layers: int, vocab: int, heads) -> dict:
+    """Attention with the Llama twin's head counts under chunks of 8,192 positions; feed-forwards in turn dense (the
+    twin's width) and routed (experts a quarter as wide: three chosen of 32, or of 16 at the larger size, and one
+    shared, so that a token's arithmetic equals the dense layer's); the last quarter of the layers reads the keys and
+    values of the layer two before."""
+    H, G, hd = heads
+    experts = 32 if width <= 2048 else 16
+    out = []
+    for i in range(layers):
+        m = {"heads": H, "kv_heads": G, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "mask": {"size": 8192},
+             "rot": {"base": 500000.0, "dims": hd}}
+        if i >= layers - max(1, layers // 4):
+            m["kv_from"] = i - 2
+        mlp = {"kind": "dense", "ff": ff, "limit": 7.0}
+        if i % 2:
+            mlp = {"kind": "moe", "expert": {"ff": ff // 4}, "shared": {"ff": ff // 4},
+                   "router": {"experts": experts, "top": 3, "scale": 2.5, "groups": {"count": 4, "keep": 2}}}
+        out.append({"type": "attention", "mixer": m, "mlp": mlp})
+    return {"architecture": "Kunulorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+            "embedding": {"scale": float(width) ** 0.5}, "layers": out}
 
 
 def llama_config(width: int, ff: int, layers: int, vocab: int, heads) -> dict:
@@ -73,6 +95,8 @@ def _measure(cfg_dict: dict, prompt_tokens: int, batch: int, steps: int, warmup:
         engine.end_sequence(s)
         if i >= warmup:
             times.append(a.elapsed_time(b))
+        elif kernels and i == warmup - 1:
+            ops.trace_report(file=open(os.devnull, "w"))       # what a kernel's first launches cost is not its time
     out = {"prefill_tokens_per_s": round(prompt_tokens / statistics.median(times) * 1e3, 1),
            "prefill_ms": round(statistics.median(times), 3)}
     if kernels:
@@ -116,17 +140,18 @@ def _table(rows, top=14):
 
 
 def run(design: str, sizes, prompt_tokens: int, batch: int, steps: int, warmup: int, kernels: bool) -> dict:
-    if design != "potuzen":
-        raise ValueError(f"no design {design!r} to compare (known: potuzen)")
+    if design not in ("potuzen", "kunulorn"):
+        raise ValueError(f"no design {design!r} to compare (known: potuzen, kunulorn)")
     result = {"design": design, "beside": "LlamaForCausalLM", "dtype": "bf16", "data": "synthetic (random weights and tokens)",
               "prompt_tokens": prompt_tokens, "decode_batch": batch, "steps": steps, "warmup": warmup, "sizes": {}}
     for name in sizes:
         width, ff, layers, vocab, heads = SIZES[name]
         t0 = time.time()
-        ours = _measure(potuzen_config(width, ff, layers, vocab), prompt_tokens, batch, steps, warmup, kernels)
+        config = potuzen_config(width, ff, layers, vocab) if design == "potuzen" else kunulorn_config(width, ff, layers, vocab, heads)
+        ours = _measure(config, prompt_tokens, batch, steps, warmup, kernels)
         twin = _measure(llama_config(width, ff, layers, vocab, heads), prompt_tokens, batch, steps, warmup, kernels)
         result["sizes"][name] = {
-            "width": width, "ff": ff, "layers": layers, "potuzen": ours, "llama": twin,
+            "width": width, "ff": ff, "layers": layers, design: ours, "llama": twin,
             "prefill_ratio": round(ours["prefill_tokens_per_s"] / twin["prefill_tokens_per_s"], 3),
             "decode_ratio": round(ours["decode_tokens_per_s"] / twin["decode_tokens_per_s"], 3)}
         print(f"[bench] {name}: {time.time() - t0:.0f} s", file=sys.stderr)

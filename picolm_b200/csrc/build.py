@@ -58,7 +58,10 @@ VARIANTS: Dict[str, Dict[str, List[str]]] = {
 MORE_BUILDS: List = [("gemm_tc_wide@stream", ["-DPLM_WIDE_STREAM"]),
                      # the gated epilogue with the tanh form of GELU in place of SiLU
                      ("gemm_tc_skinny@gelu", ["-DPLM_GATE_GELU"]), ("gemm_tc_wide@gelu", ["-DPLM_GATE_GELU"]),
-                     ("gemm_tc_wide@stream_gelu", ["-DPLM_WIDE_STREAM", "-DPLM_GATE_GELU"])]
+                     ("gemm_tc_wide@stream_gelu", ["-DPLM_WIDE_STREAM", "-DPLM_GATE_GELU"]),
+                     # the gated epilogue with clamped branches and a sloped sigmoid (its constants come with the launch)
+                     ("gemm_tc_skinny@clamped", ["-DPLM_GATE_CLAMPED"]), ("gemm_tc_wide@clamped", ["-DPLM_GATE_CLAMPED"]),
+                     ("gemm_tc_wide@stream_clamped", ["-DPLM_WIDE_STREAM", "-DPLM_GATE_CLAMPED"])]
 
 
 def attention_variant(head_dim: int, family: str = "attention_mma"):

@@ -553,10 +553,73 @@ layernorm_kernel(float* __restrict__ x, const float* __restrict__ delta, const f
     for (int i = threadIdx.x; i < d; i += NT) o[i] = from_f32<To>((row_sm[i] - mean) * scale * to_f32<Tw>(w[i]));
 }
 
+// Four elements at a time, the row kept in registers between the passes: for rows whose width is a multiple of 4 and
+// at most 16 * NT (and 16-byte aligned pointers).
+template <typename Tw, typename To, int NT>
+__global__ void __launch_bounds__(NT)
+layernorm_vec_kernel(float* __restrict__ x, const float* __restrict__ delta, const float* __restrict__ bias,
+                     const Tw* __restrict__ w, To* __restrict__ out, const int* __restrict__ rows, int d, float eps,
+                     int write_back) {
+    __shared__ float red[33];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int r = blockIdx.x;
+    const int src = rows ? PLM_ROW_NO(rows[r]) : r;
+    float* xr = x + (size_t)src * d;
+    const float* dr = delta ? delta + (size_t)src * d : nullptr;
+    float4 v[4];
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int i = (threadIdx.x + k * NT) * 4;
+        if (i < d) {
+            v[k] = load4(xr + i);
+            if (dr) {
+                const float4 dv = load4(dr + i);
+                v[k].x += dv.x; v[k].y += dv.y; v[k].z += dv.z; v[k].w += dv.w;
+            }
+            if (bias) {
+                const float4 bv = load4(bias + i);
+                v[k].x += bv.x; v[k].y += bv.y; v[k].z += bv.z; v[k].w += bv.w;
+            }
+            if (write_back) store4(xr + i, v[k]);
+            s += (v[k].x + v[k].y) + (v[k].z + v[k].w);
+        }
+    }
+    const float mean = block_sum<NT>(s, red) / (float)d;
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int i = (threadIdx.x + k * NT) * 4;
+        if (i < d) {
+            v[k].x -= mean; v[k].y -= mean; v[k].z -= mean; v[k].w -= mean;
+            ss += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+        }
+    }
+    ss = block_sum<NT>(ss, red);
+    const float scale = 1.0f / sqrtf(ss / (float)d + eps);
+    To* o = out + (size_t)r * d;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int i = (threadIdx.x + k * NT) * 4;
+        if (i < d) {
+            const float4 wv = load4(w + i);
+            store4(o + i, make_float4(v[k].x * scale * wv.x, v[k].y * scale * wv.y, v[k].z * scale * wv.z, v[k].w * scale * wv.w));
+        }
+    }
+}
+
 template <typename Tw, typename To>
 static int layernorm_launch(float* x, const float* delta, const float* bias, const void* w, void* out, const int* rows,
                             int n_rows, int d, float eps, int write_back, cudaStream_t stream) {
-    // the block size (and with it the order of the sums) depends on the row's width only
+    // the kernel and the block size (and with them the order of the sums) depend on the row's width only
+    if (d % 4 == 0 && d <= 16 * 1024 && ((((uintptr_t)x | (uintptr_t)delta | (uintptr_t)bias | (uintptr_t)w | (uintptr_t)out) & 15) == 0)) {
+        if (d <= 16 * 256)
+            return plm_status_of(launch_pdl(layernorm_vec_kernel<Tw, To, 256>, n_rows, 256, 0, stream, x, delta, bias, (const Tw*)w,
+                                            (To*)out, rows, d, eps, write_back));
+        return plm_status_of(launch_pdl(layernorm_vec_kernel<Tw, To, 1024>, n_rows, 1024, 0, stream, x, delta, bias, (const Tw*)w,
+                                        (To*)out, rows, d, eps, write_back));
+    }
     const size_t smem = (size_t)d * sizeof(float);
     if (d > 1024) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(layernorm_kernel<Tw, To, 1024>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -29,6 +29,7 @@ using namespace plm_tc;
 namespace {
 
 constexpr int EPI_STORE = 0, EPI_SWIGLU = 1, EPI_RESIDUAL = 2;
+inline Fuse with_gate(Fuse f) { f.gate_limit = g_gate_limit; f.gate_slope = g_gate_slope; return f; }
 // ring depth: with the buffer that receives the partial sums (bn x 128 floats), two CTAs of any tile
 // width fit one SM (2 x ~105 KB)
 __host__ __device__ constexpr int stages_of(int bn) { return bn <= 16 ? 5 : (bn <= 32 ? 4 : 3); }
@@ -320,8 +321,8 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                     u.x *= sc; u.y *= sc; u.z *= sc; u.w *= sc;
                 }
                 if (EPI == EPI_SWIGLU) {
-                    v[0] = swiglu_bf16(v[0], u.x); v[1] = swiglu_bf16(v[1], u.y);
-                    v[2] = swiglu_bf16(v[2], u.z); v[3] = swiglu_bf16(v[3], u.w);
+                    v[0] = swiglu_bf16(v[0], u.x, fz.gate_limit, fz.gate_slope); v[1] = swiglu_bf16(v[1], u.y, fz.gate_limit, fz.gate_slope);
+                    v[2] = swiglu_bf16(v[2], u.z, fz.gate_limit, fz.gate_slope); v[3] = swiglu_bf16(v[3], u.w, fz.gate_limit, fz.gate_slope);
                 }
                 __nv_bfloat162 o01 = __floats2bfloat162_rn(v[0], v[1]), o23 = __floats2bfloat162_rn(v[2], v[3]);
                 uint2 o;
@@ -360,7 +361,7 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
             if (fo >= F / 2) continue;
             float g = received(c, 0, pr), u = received(c, HALVES - 1, pr);
             if (SCALE) { g *= s_scale[c]; u *= s_scale[c]; }
-            out[(size_t)t * ldo + fo] = from_f32<OutT>(swiglu_bf16(g, u));
+            out[(size_t)t * ldo + fo] = from_f32<OutT>(swiglu_bf16(g, u, fz.gate_limit, fz.gate_slope));
         }
     }
     __syncthreads();                                               // reconverge before the aligned barrier
@@ -386,7 +387,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, OutT* out, int F, int T
     const int n_kb = (K + BK - 1) / BK;
     const int per = (n_kb + S - 1) / S;
     return plm_status_of(launch_pdl_cluster(kern, dim3((F + BM - 1) / BM, 1, S), dim3(NUM_THREADS), dim3(1, 1, S), smem, stream,
-                                            mw, mx, out, F, T, K, ldo, per, status, fz));
+                                            mw, mx, out, F, T, K, ldo, per, status, with_gate(fz)));
 }
 
 // ---- The walk: products with more tiles than two CTAs an SM hold at once (the LM head: 1,002 tiles of 128 rows

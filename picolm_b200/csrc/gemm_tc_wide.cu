@@ -278,7 +278,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                     OutT* __restrict__ out, int T, int F, int K, long ldo, int m_tiles, int n_tiles,
                     int* __restrict__ status, int k_splits, int kb_per_split, size_t split_stride,
-                    float* parts, int* flags, const __grid_constant__ CUtensorMap map_out, int out_by_copies) {
+                    float* parts, int* flags, const __grid_constant__ CUtensorMap map_out, int out_by_copies,
+                    const int* __restrict__ tile_group, int group_rows, float gate_limit, float gate_slope) {
+    // tile_group (grouped form, null otherwise): the weights are `groups` matrices of group_rows rows one below the
+    // other, and the token rows of tile m (128 rows) meet matrix tile_group[m] (below 0: matrix 0, rows nobody reads):
+    // the weight rows that the producer asks for start group_rows * tile_group[m] further down.  An earlier kernel
+    // of the step writes tile_group, so it is read behind pdl_wait().
     static_assert(!PAIR || BN == 256 || BN == 192, "a pair works on tiles of 256 tokens x 256 or 192 features");
     static_assert(!PAIR || TWO, "pairs take two tiles of K per stage");
     static_assert(PAIR || !TWO || BN == 128, "single CTAs take two tiles of K per stage on 128-column tiles only");
@@ -358,7 +363,13 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             Walk walk = walk0;
             Piece w;
             while (ok && walk.next(w)) {
-                const int m0 = (w.tile % m_tiles) * TILE_M + (int)rank * BM, f0 = (w.tile / m_tiles) * BN + (int)rank * W_ROWS;
+                const int m0 = (w.tile % m_tiles) * TILE_M + (int)rank * BM;
+                int f0 = (w.tile / m_tiles) * BN + (int)rank * W_ROWS;
+                if (tile_group) {
+                    if (!waited) { pdl_wait(); waited = true; }
+                    const int grp = tile_group[w.tile % m_tiles];
+                    f0 += (grp > 0 ? grp : 0) * group_rows;
+                }
                 // The stream walk takes a tile's K blocks in a turned order (a sum in any order), chosen so that
                 // all CTAs are at the same few places of K at the same time, as CTAs that walk whole tiles are:
                 // what one SM asks the L2 for, others ask for too.  A tile cut between CTAs starts where its
@@ -593,7 +604,7 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                         }
 #pragma unroll
                         for (int i = 0; i < 32; ++i)
-                            gt[i] = __float_as_uint(swiglu_bf16(__uint_as_float(gt[i]), __uint_as_float(up[i])));
+                            gt[i] = __float_as_uint(swiglu_bf16(__uint_as_float(gt[i]), __uint_as_float(up[i]), gate_limit, gate_slope));
                         if (out_by_copies) {
                             const uint32_t piece = epi_smem + (uint32_t)(((gq >> 7) & 1) * OUT_PIECE);
                             if (cc == 0) {
@@ -809,7 +820,7 @@ int launch_pair(const CUtensorMap& mx, const CUtensorMap& mw, OutT* out, int T, 
                                             out, T, F, K, ldo, m_tiles, n_tiles, status, 1,
                                             (K + BK * PAIR_SLABS - 1) / (BK * PAIR_SLABS), (size_t)0,
                                             streamed_pairs ? parts : (float*)nullptr, streamed_pairs ? flags : (int*)nullptr,
-                                            mo.map, mo.usable));
+                                            mo.map, mo.usable, (const int*)nullptr, 0, g_gate_limit, g_gate_slope));
 }
 
 // The parts and flags of the stream walk (see Walk): `slots` slots of BM * 256 floats and as many flags, which
@@ -843,7 +854,8 @@ int stream_ctas(int tiles, int n_kb, const StreamSpace& space, int group = 1, in
 template <int BN, int EPI, typename OutT, bool TWO = false>
 int launch(const CUtensorMap& mx, const CUtensorMap& mw, OutT* out, int T, int F, int K, long ldo, int* status,
            cudaStream_t stream, int k_splits = 1, int kb_per_split = 0, size_t split_stride = 0,
-           StreamSpace space = StreamSpace{nullptr, nullptr, 0}, int streamed = 0) {
+           StreamSpace space = StreamSpace{nullptr, nullptr, 0}, int streamed = 0, const int* tile_group = nullptr,
+           int group_rows = 0) {
     static bool configured = false;
     constexpr size_t smem = wide_smem(BN, EPI);
     auto kern = gemm_tc_wide_kernel<BN, EPI, OutT, false, TWO>;
@@ -864,7 +876,7 @@ int launch(const CUtensorMap& mx, const CUtensorMap& mw, OutT* out, int T, int F
     return plm_status_of(launch_pdl(kern, dim3(ctas), dim3(NUM_THREADS), smem, stream, mx, mw, out, T, F, K, ldo, m_tiles,
                                     n_tiles, status, k_splits, kb_per_split, split_stride,
                                     streamed ? space.parts : (float*)nullptr, streamed ? space.flags : (int*)nullptr,
-                                    mo.map, mo.usable));
+                                    mo.map, mo.usable, tile_group, group_rows, g_gate_limit, g_gate_slope));
 }
 
 // out[i] = sum over the K splits of scratch[s * stride + i], in order; four at a time.
@@ -996,6 +1008,36 @@ extern "C" int plm_gemm_tc_wide_space(const void* x, const void* w, void* out, i
     if (out_dtype == PLM_F32) return PLM_WIDE_LAUNCH(EPI_STORE, float, (float*)out, ldo, 1, 0, (size_t)0);
     return PLM_WIDE_LAUNCH(EPI_STORE, bf16, (bf16*)out, ldo, 1, 0, (size_t)0);
 #undef PLM_WIDE_LAUNCH
+}
+
+// The grouped form: `groups` weight matrices [F, K] one below the other in `w`, and every tile of 128 rows of x meets
+// the matrix that tile_group[tile] names (int32 on the device, written by an earlier kernel of the stream; below 0:
+// a tile nobody reads).  T is a multiple of 128.  Epilogues 0 (store) and 1 (SwiGLU); whole tiles by single CTAs.
+extern "C" int plm_gemm_tc_wide_grouped(const void* x, const void* w, void* out, int out_dtype, int epilogue, int T, int F,
+                                        int K, long ldx, long ldw, long ldo, int groups, const int* tile_group, int* status,
+                                        cudaStream_t stream) {
+    if (T <= 0 || F <= 0) return PLM_OK;
+    if (!operands_ok(x, w, K, ldx, ldw)) return PLM_ERR_ALIGN;
+    if (T % BM || groups <= 0 || tile_group == nullptr) return PLM_ERR_SHAPE;
+    if (epilogue == EPI_SWIGLU && (F % 128 || out_dtype != PLM_BF16)) return PLM_ERR_SHAPE;
+    if (epilogue != EPI_STORE && epilogue != EPI_SWIGLU) return PLM_ERR_UNSUPPORTED;
+    if (out_dtype != PLM_F32 && out_dtype != PLM_BF16) return PLM_ERR_DTYPE;
+    const StreamSpace none{nullptr, nullptr, 0};
+    const Plan plan = wide_plan(T, F, K, epilogue, none);
+    const int bn = plan.bn;
+    const bool two = plan.slabs == 2;
+    CUtensorMap mx, mw;
+    int rc;
+    if ((rc = make_map(&mx, x, T, K, ldx, BM, plan.slabs)) != PLM_OK) return rc;
+    if ((rc = make_map(&mw, w, (long)groups * F, K, ldw, bn, plan.slabs)) != PLM_OK) return rc;
+#define PLM_GROUPED_LAUNCH(EPI, OutT, outp)                                                                              \
+    (bn == 256 ? launch<256, EPI, OutT, false>(mx, mw, outp, T, F, K, ldo, status, stream, 1, 0, (size_t)0, none, 0, tile_group, F)  \
+     : two     ? launch<128, EPI, OutT, true>(mx, mw, outp, T, F, K, ldo, status, stream, 1, 0, (size_t)0, none, 0, tile_group, F)   \
+               : launch<128, EPI, OutT, false>(mx, mw, outp, T, F, K, ldo, status, stream, 1, 0, (size_t)0, none, 0, tile_group, F))
+    if (epilogue == EPI_SWIGLU) return PLM_GROUPED_LAUNCH(EPI_SWIGLU, bf16, (bf16*)out);
+    if (out_dtype == PLM_F32) return PLM_GROUPED_LAUNCH(EPI_STORE, float, (float*)out);
+    return PLM_GROUPED_LAUNCH(EPI_STORE, bf16, (bf16*)out);
+#undef PLM_GROUPED_LAUNCH
 }
 
 // The same without any workspace: K is never cut and tiles are handed out whole.

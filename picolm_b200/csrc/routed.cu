@@ -114,6 +114,42 @@ route_topk_kernel(const float* __restrict__ logits, int ld, const float* __restr
     }
 }
 
+// ------------------------------------------------------------------ the router's logits
+// out[t, e] = sum_k h[t, k] w[e, k] in fp32 for a handful of rows of w (the experts' router rows and a gate's): four
+// tokens a block with their rows of h in shared memory as fp32, a warp per row of w, lanes over k and a shuffle tree at
+// the end, so that a logit's sum has the same order in every batch.
+constexpr int RL_TOKENS = 4, RL_WARPS = 8;
+template <typename Th, typename Tw>
+__global__ void __launch_bounds__(RL_WARPS * 32)
+router_logits_kernel(const Th* __restrict__ h, const Tw* __restrict__ w, float* __restrict__ out, int T, int E, int K) {
+    extern __shared__ float rl_sm[];                // [RL_TOKENS][K]
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t0 = blockIdx.x * RL_TOKENS, nt = min(RL_TOKENS, T - t0);
+    for (int i = threadIdx.x; i < RL_TOKENS * K; i += RL_WARPS * 32) {
+        const int tt = i / K, k = i - tt * K;
+        rl_sm[i] = tt < nt ? to_f32<Th>(h[(size_t)(t0 + tt) * K + k]) : 0.f;
+    }
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int e = warp; e < E; e += RL_WARPS) {
+        const Tw* wr = w + (size_t)e * K;
+        float acc[RL_TOKENS];
+#pragma unroll
+        for (int tt = 0; tt < RL_TOKENS; ++tt) acc[tt] = 0.f;
+        for (int k = lane; k < K; k += 32) {
+            const float wv = to_f32<Tw>(wr[k]);
+#pragma unroll
+            for (int tt = 0; tt < RL_TOKENS; ++tt) acc[tt] = fmaf(rl_sm[tt * K + k], wv, acc[tt]);
+        }
+#pragma unroll
+        for (int tt = 0; tt < RL_TOKENS; ++tt) {
+            const float v = warp_sum(acc[tt]);
+            if (lane == 0 && tt < nt) out[(size_t)(t0 + tt) * E + e] = v;
+        }
+    }
+}
+
 // ---------------------------------------------------------------------- the sort
 // One block.  ids [n_entries] -> sorted [max_tiles * BM] (entry or -1), tile_expert [max_tiles] (expert or -1),
 // where [n_entries] the row of `sorted` that holds the entry.  Where an entry lands inside its expert's rows depends on
@@ -177,10 +213,14 @@ moe_align_kernel(const int* __restrict__ ids, int n_entries, int E, int BM, int*
 //   out[tile * BM + r, n] = sum in fp32 (the weighted sum per token comes after).
 constexpr int MG_BN = 64, MG_BK = 16;
 
+// where gate row n and up row n of an expert lie in its [2 N, K] matrix
+__device__ __forceinline__ int gate_row_of(int n, int N, int interleaved) { return interleaved ? (n >> 6) * 128 + (n & 63) : n; }
+__device__ __forceinline__ int up_row_of(int n, int N, int interleaved) { return interleaved ? (n >> 6) * 128 + 64 + (n & 63) : N + n; }
+
 template <typename Ta, typename Tw, typename To, int BM, int MODE>
 __global__ void __launch_bounds__(256)
 moe_gemm_kernel(const Ta* __restrict__ a, long lda, int top, const Tw* __restrict__ w, To* __restrict__ out, long ldo,
-                const int* __restrict__ tile_expert, const int* __restrict__ sorted, int N, int K) {
+                const int* __restrict__ tile_expert, const int* __restrict__ sorted, int N, int K, int interleaved) {
     constexpr int TM = BM / 16;
     __shared__ float As[MG_BK][BM + 1];
     __shared__ float Bs[MODE == 0 ? 2 : 1][MG_BK][MG_BN + 1];
@@ -214,8 +254,9 @@ moe_gemm_kernel(const Ta* __restrict__ a, long lda, int top, const Tw* __restric
         for (int idx = tid; idx < MG_BN * MG_BK; idx += 256) {
             const int n = idx / MG_BK, k = idx - n * MG_BK;
             const bool ok = n0 + n < N && k0 + k < K;
-            Bs[0][k][n] = ok ? to_f32<Tw>(wg[(size_t)(n0 + n) * K + k0 + k]) : 0.f;
-            if (MODE == 0) Bs[MODE == 0 ? 1 : 0][k][n] = ok ? to_f32<Tw>(wg[(size_t)(N + n0 + n) * K + k0 + k]) : 0.f;
+            const int row_g = MODE == 0 ? gate_row_of(n0 + n, N, interleaved) : n0 + n;
+            Bs[0][k][n] = ok ? to_f32<Tw>(wg[(size_t)row_g * K + k0 + k]) : 0.f;
+            if (MODE == 0) Bs[MODE == 0 ? 1 : 0][k][n] = ok ? to_f32<Tw>(wg[(size_t)up_row_of(n0 + n, N, interleaved) * K + k0 + k]) : 0.f;
         }
         __syncthreads();
 #pragma unroll
@@ -249,6 +290,113 @@ moe_gemm_kernel(const Ta* __restrict__ a, long lda, int top, const Tw* __restric
                 o[n] = from_f32<To>(g / (1.0f + expf(-g)) * u);
             } else {
                 o[n] = from_f32<To>(acc[0][i][j]);
+            }
+        }
+    }
+}
+
+// ------------------------------------------------ the experts' products (mma.sync, few rows an expert)
+// The same two products for bfloat16 where an expert has few rows (decode steps): a tile of 16 sorted rows times 128
+// columns of its expert's weights on `mma.sync.m16n8k16`, fp32 sums.  The weights are what the kernel moves (every
+// element is used once per tile), so they go from global memory straight into the B fragments, 16 bytes a thread and
+// row (eight consecutive k: two MMA steps, with the tile's rows read from shared memory in the same order of k);
+// the 16 rows sit in shared memory in pieces of 1,024 columns of K.  A row's sum has the same order wherever the row
+// lands.  N a multiple of 8, K a multiple of 32.
+constexpr int MM_WARPS = 8, MM_NB = 2, MM_BN = MM_WARPS * MM_NB * 8, MM_KC = 1024, MM_LD = MM_KC + 32;
+
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                               uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+
+template <int MODE>
+__global__ void __launch_bounds__(MM_WARPS * 32)
+moe_gemm_mma_kernel(const bf16* __restrict__ a, long lda, int top, const bf16* __restrict__ w, void* __restrict__ out_, long ldo,
+                    const int* __restrict__ tile_expert, const int* __restrict__ sorted, int N, int K, int interleaved) {
+    constexpr int BM = 16, NACC = MODE == 0 ? 2 : 1;
+    extern __shared__ __align__(16) uint8_t mm_raw[];
+    bf16* As = reinterpret_cast<bf16*>(mm_raw);                        // [16][MM_LD]
+    __shared__ long a_off[BM];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int tile = blockIdx.x;
+    const int e = tile_expert[tile];
+    if (e < 0) return;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
+    if (tid < BM) {
+        const int entry = sorted[tile * BM + tid];
+        a_off[tid] = entry < 0 ? -1 : (MODE == 0 ? (long)(entry / top) * lda : (long)(tile * BM + tid) * lda);
+    }
+    const bf16* we = w + (size_t)e * NACC * N * K;
+    const int n_base = blockIdx.y * MM_BN + warp * MM_NB * 8;
+    // the weight rows this thread reads: column n_base + 8 j + g of gate (and up)
+    const bf16* wrow[NACC][MM_NB];
+    bool col_ok[MM_NB];
+#pragma unroll
+    for (int j = 0; j < MM_NB; ++j) {
+        const int n = n_base + 8 * j + g;
+        col_ok[j] = n < N;
+        const int nn = col_ok[j] ? n : 0;
+        wrow[0][j] = we + (size_t)(MODE == 0 ? gate_row_of(nn, N, interleaved) : nn) * K + c * 8;
+        if (MODE == 0) wrow[NACC - 1][j] = we + (size_t)up_row_of(nn, N, interleaved) * K + c * 8;
+    }
+    float acc[NACC][MM_NB][4];
+#pragma unroll
+    for (int m = 0; m < NACC; ++m)
+#pragma unroll
+        for (int j = 0; j < MM_NB; ++j) acc[m][j][0] = acc[m][j][1] = acc[m][j][2] = acc[m][j][3] = 0.f;
+    __syncthreads();
+    for (int kc = 0; kc < K; kc += MM_KC) {
+        const int kn = min(MM_KC, K - kc);
+        for (int idx = tid; idx < BM * (kn / 8); idx += MM_WARPS * 32) {
+            const int r = idx / (kn / 8), k8 = idx - r * (kn / 8);
+            const long o = a_off[r];
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (o >= 0) v = *reinterpret_cast<const uint4*>(a + o + kc + k8 * 8);
+            *reinterpret_cast<uint4*>(As + r * MM_LD + k8 * 8) = v;
+        }
+        __syncthreads();
+        if (n_base < N) {
+#pragma unroll 2
+            for (int k0 = 0; k0 < kn; k0 += 32) {
+                uint4 b[NACC][MM_NB];
+#pragma unroll
+                for (int m = 0; m < NACC; ++m)
+#pragma unroll
+                    for (int j = 0; j < MM_NB; ++j) b[m][j] = __ldg(reinterpret_cast<const uint4*>(wrow[m][j] + kc + k0));
+                const uint4 lo = *reinterpret_cast<const uint4*>(As + g * MM_LD + k0 + c * 8);
+                const uint4 hi = *reinterpret_cast<const uint4*>(As + (g + 8) * MM_LD + k0 + c * 8);
+#pragma unroll
+                for (int m = 0; m < NACC; ++m)
+#pragma unroll
+                    for (int j = 0; j < MM_NB; ++j) {
+                        mma_bf16_16816(acc[m][j], lo.x, hi.x, lo.y, hi.y, b[m][j].x, b[m][j].y);
+                        mma_bf16_16816(acc[m][j], lo.z, hi.z, lo.w, hi.w, b[m][j].z, b[m][j].w);
+                    }
+            }
+        }
+        __syncthreads();
+    }
+    // c0, c1: row g, columns 2 c, 2 c + 1 of the block of eight; c2, c3: row g + 8
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int r = g + 8 * half;
+        if (a_off[r] < 0) continue;
+#pragma unroll
+        for (int j = 0; j < MM_NB; ++j) {
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int n = n_base + 8 * j + 2 * c + i;
+                if (n >= N) continue;
+                if (MODE == 0) {
+                    const float gv = __bfloat162float(__float2bfloat16_rn(acc[0][j][2 * half + i]));
+                    const float uv = __bfloat162float(__float2bfloat16_rn(acc[NACC - 1][j][2 * half + i]));
+                    reinterpret_cast<bf16*>(out_)[(size_t)(tile * BM + r) * ldo + n] = __float2bfloat16_rn(gv / (1.0f + expf(-gv)) * uv);
+                } else {
+                    reinterpret_cast<float*>(out_)[(size_t)(tile * BM + r) * ldo + n] = acc[0][j][2 * half + i];
+                }
             }
         }
     }
@@ -293,6 +441,29 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, long ldy, const 
 
 }  // namespace
 
+// logits [T, E] fp32 = h [T, K] w [E, K]^T; h and w float32 or bfloat16 each.
+extern "C" int plm_router_logits(const void* h, int h_dtype, const void* w, int w_dtype, float* out, int n_tokens, int E, int K,
+                                 cudaStream_t stream) {
+    if (n_tokens <= 0) return PLM_OK;
+    if (E <= 0 || K <= 0) return PLM_ERR_SHAPE;
+    const size_t smem = (size_t)RL_TOKENS * K * sizeof(float);
+    if (smem > 200 * 1024) return PLM_ERR_SHAPE;
+    const dim3 grid((n_tokens + RL_TOKENS - 1) / RL_TOKENS), nt(RL_WARPS * 32);
+#define RL_LAUNCH(Th_, Tw_)                                                                                            \
+    do {                                                                                                               \
+        if (smem > 48 * 1024)                                                                                          \
+            cudaFuncSetAttribute(router_logits_kernel<Th_, Tw_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        return plm_status_of(launch_pdl(router_logits_kernel<Th_, Tw_>, grid, nt, smem, stream, (const Th_*)h, (const Tw_*)w, \
+                                        out, n_tokens, E, K));                                                         \
+    } while (0)
+    if (h_dtype == PLM_F32 && w_dtype == PLM_F32) RL_LAUNCH(float, float);
+    if (h_dtype == PLM_BF16 && w_dtype == PLM_BF16) RL_LAUNCH(bf16, bf16);
+    if (h_dtype == PLM_BF16 && w_dtype == PLM_F32) RL_LAUNCH(bf16, float);
+    if (h_dtype == PLM_F32 && w_dtype == PLM_BF16) RL_LAUNCH(float, bf16);
+#undef RL_LAUNCH
+    return PLM_ERR_DTYPE;
+}
+
 extern "C" int plm_route_topk(const float* logits, int ld, const float* correction, int E, int top, int n_groups,
                               int keep, float scale, int* ids, float* weights, float* gate, int gate_col, int n_tokens,
                               cudaStream_t stream) {
@@ -328,16 +499,31 @@ extern "C" int plm_moe_align(const int* ids, int n_entries, int E, int bm, int* 
 
 // mode 0: gate/up with SiLU (a [T, K], out [max_tiles * bm, N] of a's type); mode 1: down (a [max_tiles * bm, K] of
 // `dtype`, out fp32).  bm 16 or 64.  dtype: a and w, PLM_F32 or PLM_BF16.
+// `interleaved` (mode 0): an expert's gate and up rows come in turns of 64 (64 gate rows, their 64 up rows, ...: the layout
+// of the tensor-core product with the activation in its epilogue) instead of all gate rows before all up rows.
+// bfloat16 with tiles of 16 rows, N a multiple of 8 and K of 32: the mma.sync kernel.
 extern "C" int plm_moe_gemm(const void* a, long lda, int top, const void* w, void* out, long ldo, int dtype, int mode,
-                            const int* tile_expert, const int* sorted, int max_tiles, int bm, int N, int K,
+                            const int* tile_expert, const int* sorted, int max_tiles, int bm, int N, int K, int interleaved,
                             cudaStream_t stream) {
     if (max_tiles <= 0) return PLM_OK;
     if (N <= 0 || K <= 0 || top <= 0) return PLM_ERR_SHAPE;
     if (bm != 16 && bm != 64) return PLM_ERR_UNSUPPORTED;
+    if (interleaved && (mode != 0 || N % 64)) return PLM_ERR_SHAPE;
+    if (dtype == PLM_BF16 && bm == 16 && N % 8 == 0 && K % 32 == 0 && lda % 8 == 0 && ((((uintptr_t)a | (uintptr_t)w) & 15) == 0)) {
+        const dim3 mgrid(max_tiles, (N + MM_BN - 1) / MM_BN), mnt(MM_WARPS * 32);
+        const size_t smem = (size_t)16 * MM_LD * sizeof(bf16);
+        if (mode == 0)
+            return plm_status_of(launch_pdl(moe_gemm_mma_kernel<0>, mgrid, mnt, smem, stream, (const bf16*)a, lda, top, (const bf16*)w,
+                                            out, ldo, tile_expert, sorted, N, K, interleaved));
+        if (mode == 1)
+            return plm_status_of(launch_pdl(moe_gemm_mma_kernel<1>, mgrid, mnt, smem, stream, (const bf16*)a, lda, top, (const bf16*)w,
+                                            out, ldo, tile_expert, sorted, N, K, interleaved));
+        return PLM_ERR_UNSUPPORTED;
+    }
     const dim3 grid(max_tiles, (N + MG_BN - 1) / MG_BN), nt(256);
 #define MG_LAUNCH(Ta_, To_, BM_, MODE_)                                                                              \
     return plm_status_of(launch_pdl(moe_gemm_kernel<Ta_, Ta_, To_, BM_, MODE_>, grid, nt, 0, stream, (const Ta_*)a, lda, top, \
-                                    (const Ta_*)w, (To_*)out, ldo, tile_expert, sorted, N, K))
+                                    (const Ta_*)w, (To_*)out, ldo, tile_expert, sorted, N, K, interleaved))
     if (dtype == PLM_F32) {
         if (mode == 0) { if (bm == 16) MG_LAUNCH(float, float, 16, 0); else MG_LAUNCH(float, float, 64, 0); }
         if (mode == 1) { if (bm == 16) MG_LAUNCH(float, float, 16, 1); else MG_LAUNCH(float, float, 64, 1); }

@@ -112,10 +112,19 @@ __device__ __forceinline__ void tc_wait_ld_into(uint32_t* r) {
 // With -DPLM_GATE_GELU (a build variant of the libraries that have this epilogue) the activation is the tanh form of
 // GELU instead: 0.5 g (1 + tanh(y)) = g / (1 + e^(-2y)) with y = sqrt(2/pi) (g + 0.044715 g^3), so the same two
 // special-function instructions serve.
-__device__ __forceinline__ float swiglu_bf16(float g, float u) {
+// With -DPLM_GATE_CLAMPED (another such variant) both branches are clamped, the gate's sigmoid has a slope and the up
+// branch is shifted by one: g' = min(g, limit), u' = clamp(u, -limit, limit), g' sigmoid(slope g') (u' + 1).  The two
+// constants come with the launch (plm_gate_constants sets what the next launches of this library pass on).
+__device__ __forceinline__ float swiglu_bf16(float g, float u, float limit = 0.f, float slope = 1.f) {
     g = __bfloat162float(__float2bfloat16_rn(g));
     u = __bfloat162float(__float2bfloat16_rn(u));
     float e;
+#ifdef PLM_GATE_CLAMPED
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(g * slope * -1.4426950408889634f));
+    return __fdividef(g, 1.0f + e) * (u + 1.0f);
+#endif
 #ifdef PLM_GATE_GELU
     const float y2 = 1.5957691216057308f * fmaf(0.044715f * g * g, g, g);            // 2 sqrt(2/pi) (g + 0.044715 g^3)
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(y2 * -1.4426950408889634f));
@@ -223,6 +232,17 @@ struct Fuse {
     bf16* xw;                   // EPI_RESIDUAL: [T, ld_xw]
     long ld_xw;
     float* ss_out;              // EPI_RESIDUAL: [rows as the kernel says, its own row length]
+    float gate_limit, gate_slope;   // the gated epilogue's constants (the clamped variant; see swiglu_bf16)
 };
 
+// What the gated epilogue's constants are for the launches that follow (host side; a launch takes them along as
+// arguments, so a captured launch keeps the values it was captured with).
+static float g_gate_limit = 0.f, g_gate_slope = 1.f;
+
 }  // namespace plm_tc
+
+extern "C" int plm_gate_constants(float limit, float slope) {
+    plm_tc::g_gate_limit = limit;
+    plm_tc::g_gate_slope = slope;
+    return 0;
+}

@@ -16,6 +16,6 @@ from .gemm import (PendingLinear, ScaledRows, gemm_simt, gemm_tc_skinny, gemm_tc
                    residual_norm_supported)
 from .recurrent import (DECAY_SIGMOID, DECAY_STEP, GATE_AFTER_NORM, GATE_BEFORE_NORM, GATE_NONE, causal_conv,  # noqa: F401
                         gated_norm, head_linear, linear_scan, store_rows_paged)
-from .routed import (SortedPairs, moe_align, moe_combine, moe_down, moe_gate_up, moe_gather, moe_max_tiles,  # noqa: F401
-                     route_topk)
+from .routed import (SortedPairs, moe_align, moe_combine, moe_down, moe_down_tc, moe_gate_up, moe_gate_up_tc,  # noqa: F401
+                     moe_gather, moe_max_tiles, moe_tc_supported, route_topk, router_logits)
 from .sampling import argmax, sample  # noqa: F401

@@ -27,8 +27,11 @@ _SIGNATURES = {
                                _i, _i, _i, _i, _vp],
     "plm_route_topk": [_vp, _i, _vp, _i, _i, _i, _i, _f, _vp, _vp, _vp, _i, _i, _vp],
     "plm_moe_max_tiles": [_i, _i, _i],
+    "plm_gate_constants": [_f, _f],
+    "plm_router_logits": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _vp],
     "plm_moe_align": [_vp, _i, _i, _i, _vp, _vp, _vp, _i, _vp],
-    "plm_moe_gemm": [_vp, _l, _i, _vp, _vp, _l, _i, _i, _vp, _vp, _i, _i, _i, _i, _vp],
+    "plm_moe_gemm": [_vp, _l, _i, _vp, _vp, _l, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp],
+    "plm_gemm_tc_wide_grouped": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _l, _l, _l, _i, _vp, _vp, _vp],
     "plm_moe_gather": [_vp, _vp, _vp, _i, _i, _l, _vp],
     "plm_moe_combine": [_vp, _l, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _vp],
     "plm_rope_store": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],

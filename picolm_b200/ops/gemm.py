@@ -57,13 +57,25 @@ def _gated_library(name: str, flags: tuple, activation: str):
     "gelu_tanh": the variant compiled with -DPLM_GATE_GELU)."""
     if activation == "silu":
         return name, flags
-    if activation != "gelu_tanh":
-        raise KernelError(f"the gated epilogue knows silu and gelu_tanh, not {activation!r}")
-    return (name + "_gelu" if "@" in name else name + "@gelu"), tuple(flags) + ("-DPLM_GATE_GELU",)
+    if activation not in _GATE_VARIANTS:
+        raise KernelError(f"the gated epilogue knows silu, {', '.join(_GATE_VARIANTS)}, not {activation!r}")
+    suffix, flag = _GATE_VARIANTS[activation]
+    return (name + "_" + suffix if "@" in name else name + "@" + suffix), tuple(flags) + (flag,)
+
+
+# activation -> (the variant's name, its compile flag)
+_GATE_VARIANTS = {"gelu_tanh": ("gelu", "-DPLM_GATE_GELU"), "swish_clamped": ("clamped", "-DPLM_GATE_CLAMPED")}
+
+
+def _set_gate_constants(lib, flags, activation: str, limit: float, slope: float) -> None:
+    """The clamped gate's two constants for the launches of `lib` that follow (they travel as kernel arguments)."""
+    if activation == "swish_clamped":
+        _fn(lib, "plm_gate_constants", flags)(float(limit), float(slope))
 
 
 def gemm_tc_skinny(a, w: torch.Tensor, out_dtype: torch.dtype, swiglu: bool = False,
-                   out: Optional[torch.Tensor] = None, activation: str = "silu") -> torch.Tensor:
+                   out: Optional[torch.Tensor] = None, activation: str = "silu", limit: float = 0.0,
+                   slope: float = 1.0) -> torch.Tensor:
     """The decode-shaped tensor-core product: a [M <= 64, K] @ w [N, K]^T with the weights on the MMA's 128
     rows and K split over a thread-block cluster whose CTAs add their partial tiles up through distributed
     shared memory.  With `swiglu`, w holds tiles of 64 gate rows followed by their 64 up rows (see
@@ -88,6 +100,8 @@ def gemm_tc_skinny(a, w: torch.Tensor, out_dtype: torch.dtype, swiglu: bool = Fa
     if out is None:
         out = torch.empty((M, n_out), dtype=out_dtype, device=a.device)
     lib, lib_flags = _gated_library("gemm_tc_skinny", (), activation if swiglu else "silu")
+    if swiglu:
+        _set_gate_constants(lib, lib_flags, activation, limit, slope)
     if scaled is not None:
         _check(_fn(lib, "plm_gemm_tc_skinny_scaled", lib_flags)(
             _p(a), _p(w), _p(out), 1 if swiglu else 0, M, N, K, K, K, n_out, _p(scaled.parts), scaled.parts.shape[0],
@@ -217,7 +231,7 @@ def linear_residual_norm(pending: PendingLinear, x: torch.Tensor, norm_weight: t
 
 def gemm_tc_wide(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, swiglu: bool = False,
                  out: Optional[torch.Tensor] = None, pair: bool = False, add: bool = False,
-                 activation: str = "silu") -> torch.Tensor:
+                 activation: str = "silu", limit: float = 0.0, slope: float = 1.0) -> torch.Tensor:
     """The prompt-shaped tensor-core product: a [M > 64, K] @ w [N, K]^T by a persistent tcgen05 kernel
     (one CTA per SM, two accumulators in tensor memory so that a tile's epilogue overlaps the next
     tile's main loop; where the tiles do not fill one round over the SMs and K is long, the K blocks of all
@@ -252,6 +266,8 @@ def gemm_tc_wide(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, swigl
         streamed = K % 64 == 0 and stream_space_enabled() and _pair_streamed(M, N, K) > 0
         parts, flags, slots = stream_space(a.device) if streamed else (None, None, 0)
         lib = STREAM_LIB if streamed else PLAIN_LIB
+        if swiglu:
+            _set_gate_constants(lib[0], lib[1], act, limit, slope)
         _check(_fn(lib[0], "plm_gemm_tc_pair_space", lib[1])(
             _p(a), _p(w), _p(out), _dt(out, "out"), epilogue, M, N, K, K, K, n_out, _p(parts), _p(flags), slots,
             _p(status_word(a.device)), _stream()), "gemm_tc_pair" + (" (stream)" if streamed else "") + name, **work)
@@ -268,6 +284,8 @@ def gemm_tc_wide(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, swigl
     streamed = how[2] > 0
     parts, flags, slots = stream_space(a.device) if streamed else (None, None, 0)
     lib = STREAM_LIB if streamed else PLAIN_LIB
+    if swiglu:
+        _set_gate_constants(lib[0], lib[1], act, limit, slope)
     _check(_fn(lib[0], "plm_gemm_tc_wide_space", lib[1])(
         _p(a), _p(w), _p(out), _dt(out, "out"), epilogue, M, N, K, K, K, n_out, _p(scratch), _p(parts), _p(flags), slots,
         _p(status_word(a.device)), _stream()), "gemm_tc_wide" + (" (stream)" if streamed else "") + name, kernels=kernels, **work)
@@ -328,7 +346,8 @@ def pair_pays(m: int, n: int, k: int = 0, epilogue: int = 0) -> bool:
     return _pair_streamed(m, n, k) > 0
 
 
-def linear_swiglu(a, w_gate_up: torch.Tensor, defer: bool = False, activation: str = "silu"):
+def linear_swiglu(a, w_gate_up: torch.Tensor, defer: bool = False, activation: str = "silu", limit: float = 0.0,
+                  slope: float = 1.0):
     """silu(a @ gate^T) * (a @ up^T) with `w_gate_up` from `interleave_gate_up`: one tensor-core product
     whose epilogue applies the activation ("silu", or "gelu_tanh" from a build variant of the same kernels); [M, F] in
     bfloat16.  `a` may be `ScaledRows`.  With `defer` (the
@@ -351,8 +370,9 @@ def linear_swiglu(a, w_gate_up: torch.Tensor, defer: bool = False, activation: s
     if not gemm_tc_supported(x, w_gate_up) or N % 128:
         raise KernelError("linear_swiglu: needs bfloat16 operands the tensor-core kernel takes and N % 128 == 0")
     if M <= 64:
-        return gemm_tc_skinny(a, w_gate_up, torch.bfloat16, swiglu=True, activation=activation)
-    return gemm_tc_wide(a, w_gate_up, torch.bfloat16, swiglu=True, pair=pair_pays(M, N, K, 1), activation=activation)
+        return gemm_tc_skinny(a, w_gate_up, torch.bfloat16, swiglu=True, activation=activation, limit=limit, slope=slope)
+    return gemm_tc_wide(a, w_gate_up, torch.bfloat16, swiglu=True, pair=pair_pays(M, N, K, 1), activation=activation,
+                        limit=limit, slope=slope)
 
 
 def linear(a, w: torch.Tensor, out_dtype: torch.dtype, defer: bool = False):

@@ -7,7 +7,21 @@ from typing import Optional, Tuple
 
 import torch
 
-from ._lib import KernelError, _check, _dev, _dt, _fn, _i32, _p, _stream
+from ._lib import KernelError, _check, _dev, _dt, _fn, _i32, _p, _stream, status_word
+
+
+def router_logits(h: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """h [T, K] times the few rows of w [E, K] (the experts' router rows, a gate's) as float32 [T, E]: float32 sums in an
+    order that depends on K only."""
+    _dev(h, "h"), _dev(w, "w")
+    T, K = h.shape
+    E = w.shape[0]
+    if w.shape != (E, K):
+        raise KernelError(f"router_logits: h is [{T}, {K}] but w is {tuple(w.shape)}")
+    out = torch.empty((T, E), dtype=torch.float32, device=h.device)
+    _check(_fn("routed", "plm_router_logits")(_p(h), _dt(h, "h"), _p(w), _dt(w, "w"), _p(out), T, E, K, _stream()),
+           f"router_logits {T}x{E}x{K}", flops=2 * T * E * K, nbytes=h.numel() * h.element_size())
+    return out
 
 
 def route_topk(logits: torch.Tensor, n_experts: int, top: int, correction: Optional[torch.Tensor] = None,
@@ -72,9 +86,11 @@ def moe_align(ids: torch.Tensor, n_experts: int, bm: int) -> SortedPairs:
     return SortedPairs(sorted_, tile_expert, where, bm, max_tiles, top, T)
 
 
-def moe_gate_up(h: torch.Tensor, w_gate_up: torch.Tensor, pairs: SortedPairs) -> torch.Tensor:
+def moe_gate_up(h: torch.Tensor, w_gate_up: torch.Tensor, pairs: SortedPairs, interleaved: bool = False) -> torch.Tensor:
     """silu(W_gate[e] h) * (W_up[e] h) for every sorted pair: `h` [T, d], `w_gate_up` [E, 2F, d] (an expert's F gate
-    rows, then its F up rows), both of one type; [rows, F] of that type, in sorted order."""
+    rows, then its F up rows; `interleaved`: 64 gate rows, their 64 up rows, and so on, as `interleave_gate_up` lays
+    them out), both of one type; [rows, F] of that type, in sorted order.  bfloat16 with tiles of 16 rows runs on
+    `mma.sync` (F a multiple of 8, d of 32), everything else on the CUDA cores."""
     _dev(h, "h"), _dev(w_gate_up, "w_gate_up")
     E, F2, d = w_gate_up.shape
     if h.dtype != w_gate_up.dtype or h.shape != (pairs.n_tokens, d) or F2 % 2:
@@ -83,7 +99,8 @@ def moe_gate_up(h: torch.Tensor, w_gate_up: torch.Tensor, pairs: SortedPairs) ->
     out = torch.empty((pairs.rows, F), dtype=h.dtype, device=h.device)
     _check(_fn("routed", "plm_moe_gemm")(
         _p(h), d, pairs.top, _p(w_gate_up), _p(out), F, _dt(h, "h"), 0, _p(pairs.tile_expert), _p(pairs.sorted),
-        pairs.max_tiles, pairs.bm, F, d, _stream()), f"moe_gate_up tiles<={pairs.max_tiles}x{pairs.bm} F={F} d={d}",
+        pairs.max_tiles, pairs.bm, F, d, 1 if interleaved else 0, _stream()),
+        f"moe_gate_up tiles<={pairs.max_tiles}x{pairs.bm} F={F} d={d}",
         flops=2 * pairs.n_tokens * pairs.top * F2 * d, nbytes=w_gate_up.numel() * w_gate_up.element_size())
     return out
 
@@ -97,7 +114,7 @@ def moe_down(act: torch.Tensor, w_down: torch.Tensor, pairs: SortedPairs) -> tor
     out = torch.empty((pairs.rows, d), dtype=torch.float32, device=act.device)
     _check(_fn("routed", "plm_moe_gemm")(
         _p(act), F, pairs.top, _p(w_down), _p(out), d, _dt(act, "act"), 1, _p(pairs.tile_expert), _p(pairs.sorted),
-        pairs.max_tiles, pairs.bm, d, F, _stream()), f"moe_down tiles<={pairs.max_tiles}x{pairs.bm} d={d} F={F}",
+        pairs.max_tiles, pairs.bm, d, F, 0, _stream()), f"moe_down tiles<={pairs.max_tiles}x{pairs.bm} d={d} F={F}",
         flops=2 * pairs.n_tokens * pairs.top * F * d, nbytes=w_down.numel() * w_down.element_size())
     return out
 
@@ -130,3 +147,38 @@ def moe_combine(y: torch.Tensor, pairs: SortedPairs, weights: torch.Tensor, shar
     _check(_fn("routed", "plm_moe_combine")(_p(y), d, _p(pairs.where), _p(weights), top, _p(shared), _p(gate), _p(out), T, d,
                                             _stream()), f"moe_combine T={T} d={d}", nbytes=(top + 2) * T * d * 4)
     return out
+
+
+def moe_tc_supported(h: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor) -> bool:
+    """Whether the experts' products can run on tcgen05 (`moe_gate_up_tc`, `moe_down_tc`): bfloat16, an inner width
+    that is a multiple of 64, rows that TMA can address."""
+    E, F2, d = w_gate_up.shape
+    F = F2 // 2
+    return (h.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16 and w_down.dtype == torch.bfloat16
+            and F % 64 == 0 and d % 8 == 0 and d >= 64 and w_gate_up.data_ptr() % 16 == 0 and w_down.data_ptr() % 16 == 0)
+
+
+def _grouped(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, pairs: SortedPairs, what: str) -> torch.Tensor:
+    E, N, K = w.shape
+    if pairs.bm != 128 or x.shape != (pairs.rows, K) or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError(f"{what}: tiles of 128 sorted rows [rows, {K}] in bfloat16 are expected")
+    _check(_fn("gemm_tc_wide", "plm_gemm_tc_wide_grouped")(
+        _p(x), _p(w), _p(out), _dt(out, "out"), epilogue, pairs.rows, N, K, K, K, out.shape[1], E, _p(pairs.tile_expert),
+        _p(status_word(x.device)), _stream()), f"{what} tiles<={pairs.max_tiles}x128 N={N} K={K}",
+        flops=2 * pairs.n_tokens * pairs.top * N * K, nbytes=w.numel() * 2)
+    return out
+
+
+def moe_gate_up_tc(x_sorted: torch.Tensor, w_gate_up: torch.Tensor, pairs: SortedPairs) -> torch.Tensor:
+    """`moe_gate_up` on tcgen05 for tiles of 128 rows: `x_sorted` [rows, d] from `moe_gather`, `w_gate_up` [E, 2F, d]
+    interleaved in turns of 64 rows; the activation in the product's epilogue; [rows, F] bfloat16."""
+    _dev(x_sorted, "x_sorted"), _dev(w_gate_up, "w_gate_up")
+    out = torch.empty((pairs.rows, w_gate_up.shape[1] // 2), dtype=torch.bfloat16, device=x_sorted.device)
+    return _grouped(x_sorted, w_gate_up, out, 1, pairs, "moe_gate_up_tc")
+
+
+def moe_down_tc(act: torch.Tensor, w_down: torch.Tensor, pairs: SortedPairs) -> torch.Tensor:
+    """`moe_down` on tcgen05 for tiles of 128 rows; float32 [rows, d]."""
+    _dev(act, "act"), _dev(w_down, "w_down")
+    out = torch.empty((pairs.rows, w_down.shape[1]), dtype=torch.float32, device=act.device)
+    return _grouped(act, w_down, out, 0, pairs, "moe_down_tc")

@@ -43,7 +43,7 @@ class GatedMLP(Part):
         # One projection for both branches.  Where the tensor-core product can apply the activation
         # in its epilogue, the rows are laid out in tiles of 64 gate rows and their 64 up rows;
         # otherwise plainly [gate | up] with the activation as a kernel of its own.
-        self.fused = (p["activation"] in ("silu", "gelu_tanh") and gate.dtype == torch.bfloat16 and up.dtype == torch.bfloat16 and gate.shape[0] % 64 == 0
+        self.fused = (p["activation"] in ("silu", "gelu_tanh", "swish_clamped") and gate.dtype == torch.bfloat16 and up.dtype == torch.bfloat16 and gate.shape[0] % 64 == 0
                       and gate.shape[1] % 8 == 0 and gate.shape[1] >= 64)
         self.w_gate_up = ops.interleave_gate_up(gate, up) if self.fused else _stack_rows([gate, up])
         self.w_down = tensors[p["down_name"]]
@@ -58,7 +58,8 @@ class GatedMLP(Part):
     def forward(self, h, step):
         if self.fused:
             # handed to the next product and nowhere else
-            act = ops.linear_swiglu(h, self.w_gate_up, defer=True, activation=self.params["activation"])
+            act = ops.linear_swiglu(h, self.w_gate_up, defer=True, activation=self.params["activation"],
+                                    limit=float(self.params.get("limit", 0.0)), slope=float(self.params.get("slope", 1.0)))
         else:
             act = ops.swiglu(ops.linear(h, self.w_gate_up, self.runtime.dtype), activation=self.params["activation"],
                              limit=float(self.params.get("limit", 0.0)), slope=float(self.params.get("slope", 1.0)))
@@ -136,9 +137,12 @@ class RoutedMLP(Part):
         # the router and the shared expert's gate as one float32 product: [experts (+ 1), hidden]
         self.w_router = _stack_rows(rows)
         self.correction = (tensors[p["correction_name"]].to(torch.float32).contiguous() if p.get("correction_name") else None)
-        # [E, 2F, d]: an expert's gate rows, then its up rows; [E, d, F]
-        self.w_gate_up = torch.stack([torch.cat([tensors[self._expert(e, "gate_name")], tensors[self._expert(e, "up_name")]])
-                                      for e in range(self.E)]).contiguous()
+        # [E, 2F, d]: an expert's gate rows, then its up rows (in turns of 64 where the inner width allows it: the
+        # layout of the tensor-core product with the activation in its epilogue, which every kernel here reads); [E, d, F]
+        gates, ups = [tensors[self._expert(e, "gate_name")] for e in range(self.E)], [tensors[self._expert(e, "up_name")] for e in range(self.E)]
+        self.interleaved = self.F % 64 == 0
+        self.w_gate_up = torch.stack([ops.interleave_gate_up(g, u) if self.interleaved else torch.cat([g, u])
+                                      for g, u in zip(gates, ups)]).contiguous()
         self.w_down = torch.stack([tensors[self._expert(e, "down_name")] for e in range(self.E)]).contiguous()
 
     def weight_bytes(self):
@@ -151,14 +155,21 @@ class RoutedMLP(Part):
         if hasattr(h, "materialize"):
             h = h.materialize()
         T = h.shape[0]
-        logits = ops.gemm_simt(h, self.w_router, torch.float32)
+        logits = ops.router_logits(h, self.w_router)
         ids, weights, gate = ops.route_topk(logits, self.E, self.top, self.correction, self.n_groups, self.keep,
                                             float(self.params["route_scale"]), self.gate_col)
-        # few pairs an expert (decode steps): small tiles, so that a tile's padding costs little
-        bm = 16 if T * self.top <= 16 * self.E else 64
-        pairs = ops.moe_align(ids, self.E, bm)
-        act = ops.moe_gate_up(h, self.w_gate_up, pairs)
-        y = ops.moe_down(act, self.w_down, pairs)
+        if self.interleaved and T * self.top >= 64 * self.E and ops.moe_tc_supported(h, self.w_gate_up, self.w_down):
+            # many pairs an expert (prompts): tiles of 128 rows on tcgen05, the tokens' rows laid out in sorted order first
+            pairs = ops.moe_align(ids, self.E, 128)
+            act = ops.moe_gate_up_tc(ops.moe_gather(h, pairs), self.w_gate_up, pairs)
+            y = ops.moe_down_tc(act, self.w_down, pairs)
+        else:
+            # few pairs an expert (decode steps): small tiles, so that a tile's padding costs little; bfloat16 on
+            # mma.sync, float32 on the CUDA cores (which take tiles of 64 rows where experts have many)
+            bm = 16 if (h.dtype == torch.bfloat16 or T * self.top <= 16 * self.E) else 64
+            pairs = ops.moe_align(ids, self.E, bm)
+            act = ops.moe_gate_up(h, self.w_gate_up, pairs, interleaved=self.interleaved)
+            y = ops.moe_down(act, self.w_down, pairs)
         shared = None
         if self.shared is not None:
             shared = self.shared.forward(h, step)

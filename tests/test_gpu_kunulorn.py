@@ -208,6 +208,27 @@ def test_clamped_gate_kernel(dtype):
     assert (got - want).abs().max() <= (1e-6 if dtype == torch.float32 else 8e-3)
 
 
+@pytest.mark.parametrize("T", [8, 200, 1024])
+def test_clamped_gate_in_the_products_epilogue(T):
+    """The tensor-core products with the clamped gate in their epilogue (decode-shaped, prompt-shaped, pairs of CTAs),
+    two limits one after the other (the constants travel with each launch), and the router's logits kernel."""
+    from picolm_b200 import ops
+    g = torch.Generator().manual_seed(T)
+    F, K = 512, 256
+    x = torch.randn(T, K, generator=g).to(torch.bfloat16)
+    wg, wu = (torch.randn(F, K, generator=g) * 0.1).to(torch.bfloat16), (torch.randn(F, K, generator=g) * 0.1).to(torch.bfloat16)
+    w = ops.interleave_gate_up(wg.to(DEV), wu.to(DEV))
+    for limit in (0.6, 2.5):
+        gate = (x.double() @ wg.double().T).to(torch.bfloat16).double().clamp(max=limit)
+        up = (x.double() @ wu.double().T).to(torch.bfloat16).double().clamp(-limit, limit)
+        want = gate * torch.sigmoid(1.702 * gate) * (up + 1)
+        got = ops.linear_swiglu(x.to(DEV), w, activation="swish_clamped", limit=limit, slope=1.702).cpu().double()
+        assert (got - want).abs().max() <= 2e-2 * want.abs().max(), f"limit {limit}"
+    logits = ops.router_logits(x.to(DEV), wg[:37].contiguous().to(DEV)).cpu().double()
+    assert (logits - x.double() @ wg[:37].double().T).abs().max() < 1e-4
+    ops.check_status()
+
+
 @pytest.mark.parametrize("E,top,groups,scale", [(16, 3, (4, 2), 1.5), (6, 2, (3, 2), 1.0), (8, 1, None, 2.5), (6, 2, (6, 3), 1.0),
                                                 (12, 4, (1, 1), 0.5), (64, 6, (8, 3), 2.0)])
 def test_router_choice_kernel(E, top, groups, scale):
@@ -272,6 +293,42 @@ def test_experts_products_over_sorted_pairs(T, E, top, F, d, dtype):
         assert (got - want).abs().max() <= tol * want.abs().max(), f"tiles of {bm}"
         gathered = ops.moe_gather(h.to(DEV), pairs).cpu()
         assert torch.equal(gathered[pairs.where.cpu().long()], h[torch.arange(T * top) // top])
+
+
+@pytest.mark.parametrize("T,E,top,F,d", [(300, 4, 2, 128, 128), (40, 8, 3, 64, 96), (700, 3, 1, 192, 320)])
+def test_experts_products_on_the_tensor_cores(T, E, top, F, d):
+    """bfloat16 with an inner width that is a multiple of 64: gate and up rows in turns of 64, tiles of 16 rows on
+    mma.sync and tiles of 128 rows on tcgen05 (the rows laid out in sorted order first), against a loop over tokens."""
+    from picolm_b200 import ops
+    g = torch.Generator().manual_seed(T + F)
+    bf = torch.bfloat16
+    h = torch.randn(T, d, generator=g).to(bf)
+    wg, wu = (torch.randn(E, F, d, generator=g) * 0.2).to(bf), (torch.randn(E, F, d, generator=g) * 0.2).to(bf)
+    wd = (torch.randn(E, d, F, generator=g) * 0.2).to(bf)
+    ids = torch.stack([torch.randperm(E, generator=g)[:top] for _ in range(T)]).to(torch.int32)
+    ids[: T // 2, 0] = E - 1                                             # one expert far busier than the others,
+    if top > 1:
+        ids[: T // 2, 1:] = torch.arange(top - 1)[None]
+    if E > 3:
+        ids[ids == 1] = 2 if top == 1 else ids[ids == 1]                    # (and, where it can be, one without any row)
+    weights = torch.rand(T, top, generator=g)
+    want = torch.zeros(T, d, dtype=torch.float64)
+    for t in range(T):
+        for k in range(top):
+            e = int(ids[t, k])
+            want[t] += weights[t, k].double() * P.expert(h[t:t + 1].double(), wg[e].double(), wu[e].double(), wd[e].double())[0]
+    w_gu = torch.stack([ops.interleave_gate_up(a.to(DEV), b.to(DEV)) for a, b in zip(wg, wu)]).contiguous()
+    hd, wdd = h.to(DEV), wd.to(DEV)
+    assert ops.moe_tc_supported(hd, w_gu, wdd)
+    small = ops.moe_align(ids.to(DEV), E, 16)
+    y = ops.moe_down(ops.moe_gate_up(hd, w_gu, small, interleaved=True), wdd, small)
+    got = ops.moe_combine(y, small, weights.to(DEV)).cpu().double()
+    assert (got - want).abs().max() <= 2e-2 * want.abs().max(), "tiles of 16 rows (mma.sync)"
+    big = ops.moe_align(ids.to(DEV), E, 128)
+    y = ops.moe_down_tc(ops.moe_gate_up_tc(ops.moe_gather(hd, big), w_gu, big), wdd, big)
+    got2 = ops.moe_combine(y, big, weights.to(DEV)).cpu().double()
+    assert (got2 - want).abs().max() <= 2e-2 * want.abs().max(), "tiles of 128 rows (tcgen05)"
+    ops.check_status()
 
 
 def _attention_plain(q, k, v, pos_q, scale, chunk):
