@@ -117,8 +117,9 @@ def _measure(cfg_dict: dict, prompt_tokens: int, batch: int, steps: int, warmup:
     torch.cuda.synchronize()
     ms = a.elapsed_time(b) / steps
     out.update(decode_tokens_per_s=round(batch / ms * 1e3, 1), decode_ms_per_step=round(ms, 4), decode_batch=batch,
-               decode_from_graph=bool(engine._graphs), weight_gb=round(engine.model.weight_bytes_per_step() / 1e9, 3))
-    out["decode_hbm_frac"] = round(engine.model.weight_bytes_per_step() / (ms * 1e-3) / (ops._lib.PEAK_GBS * 1e9), 3)
+               decode_from_graph=bool(engine._graphs), weight_gb=round(engine.model.weight_bytes_per_step(batch) / 1e9, 3))
+    # (a routed feed-forward counts min(experts, batch x top) experts a layer: what the batch reads at most)
+    out["decode_hbm_frac"] = round(engine.model.weight_bytes_per_step(batch) / (ms * 1e-3) / (ops._lib.PEAK_GBS * 1e9), 3)
     if kernels:
         out["decode_kernels"] = _table(ops.trace_report(file=open(os.devnull, "w")))
     for s in slots:

@@ -281,7 +281,7 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                     float* parts, int* flags, const __grid_constant__ CUtensorMap map_out, int out_by_copies,
                     const int* __restrict__ tile_group, int group_rows, float gate_limit, float gate_slope) {
     // tile_group (grouped form, null otherwise): the weights are `groups` matrices of group_rows rows one below the
-    // other, and the token rows of tile m (128 rows) meet matrix tile_group[m] (below 0: matrix 0, rows nobody reads):
+    // other, and the token rows of tile m (128 rows) meet matrix tile_group[m] (below 0: a tile without rows, which is passed by):
     // the weight rows that the producer asks for start group_rows * tile_group[m] further down.  An earlier kernel
     // of the step writes tile_group, so it is read behind pdl_wait().
     static_assert(!PAIR || BN == 256 || BN == 192, "a pair works on tiles of 256 tokens x 256 or 192 features");
@@ -368,7 +368,8 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 if (tile_group) {
                     if (!waited) { pdl_wait(); waited = true; }
                     const int grp = tile_group[w.tile % m_tiles];
-                    f0 += (grp > 0 ? grp : 0) * group_rows;
+                    if (grp < 0) continue;                               // a tile without rows: every role passes it by
+                    f0 += grp * group_rows;
                 }
                 // The stream walk takes a tile's K blocks in a turned order (a sum in any order), chosen so that
                 // all CTAs are at the same few places of K at the same time, as CTAs that walk whole tiles are:
@@ -436,7 +437,9 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 #ifdef PLM_WIDE_TRACE
             long long waited_full = 0, m_begin = clock64();
 #endif
+            if (tile_group) pdl_wait();                                  // an earlier kernel of the step writes it
             for (; ok && walk.next(w); ++j) {
+                if (tile_group && tile_group[w.tile % m_tiles] < 0) { --j; continue; }
                 const int acc = j & 1;
                 // the epilogue must have read this accumulator's previous piece out
                 if (!mbar_wait(acc_empty0 + 8 * acc, ((j >> 1) & 1) ^ 1, status, 2)) { s_abort = 1; ok = false; break; }
@@ -486,6 +489,7 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         Walk walk = walk0;
         Piece w;
         for (; ok && walk.next(w); ++j) {
+            if (tile_group && tile_group[w.tile % m_tiles] < 0) { --j; continue; }
             const int acc = j & 1;
             const int m0 = (w.tile % m_tiles) * TILE_M + (int)rank * BM, f0 = (w.tile / m_tiles) * BN;
             const int row0 = m0 + quarter * 32;                          // this warp's 32 token rows
@@ -1012,7 +1016,7 @@ extern "C" int plm_gemm_tc_wide_space(const void* x, const void* w, void* out, i
 
 // The grouped form: `groups` weight matrices [F, K] one below the other in `w`, and every tile of 128 rows of x meets
 // the matrix that tile_group[tile] names (int32 on the device, written by an earlier kernel of the stream; below 0:
-// a tile nobody reads).  T is a multiple of 128.  Epilogues 0 (store) and 1 (SwiGLU); whole tiles by single CTAs.
+// a tile without rows, which is passed by and whose rows of `out` are left as they are).  T is a multiple of 128.  Epilogues 0 (store) and 1 (SwiGLU); whole tiles by single CTAs.
 extern "C" int plm_gemm_tc_wide_grouped(const void* x, const void* w, void* out, int out_dtype, int epilogue, int T, int F,
                                         int K, long ldx, long ldw, long ldo, int groups, const int* tile_group, int* status,
                                         cudaStream_t stream) {

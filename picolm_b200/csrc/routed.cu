@@ -116,8 +116,8 @@ route_topk_kernel(const float* __restrict__ logits, int ld, const float* __restr
 
 // ------------------------------------------------------------------ the router's logits
 // out[t, e] = sum_k h[t, k] w[e, k] in fp32 for a handful of rows of w (the experts' router rows and a gate's): four
-// tokens a block with their rows of h in shared memory as fp32, a warp per row of w, lanes over k and a shuffle tree at
-// the end, so that a logit's sum has the same order in every batch.
+// tokens a block with their rows of h in shared memory as fp32, a warp per row of w (blockIdx.y: which eight rows), lanes
+// over k and a shuffle tree at the end, so that a logit's sum has the same order in every batch.
 constexpr int RL_TOKENS = 4, RL_WARPS = 8;
 template <typename Th, typename Tw>
 __global__ void __launch_bounds__(RL_WARPS * 32)
@@ -132,11 +132,12 @@ router_logits_kernel(const Th* __restrict__ h, const Tw* __restrict__ w, float* 
     }
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int e = warp; e < E; e += RL_WARPS) {
+    for (int e = blockIdx.y * RL_WARPS + warp; e < E; e += gridDim.y * RL_WARPS) {
         const Tw* wr = w + (size_t)e * K;
         float acc[RL_TOKENS];
 #pragma unroll
         for (int tt = 0; tt < RL_TOKENS; ++tt) acc[tt] = 0.f;
+#pragma unroll 4
         for (int k = lane; k < K; k += 32) {
             const float wv = to_f32<Tw>(wr[k]);
 #pragma unroll
@@ -448,7 +449,7 @@ extern "C" int plm_router_logits(const void* h, int h_dtype, const void* w, int 
     if (E <= 0 || K <= 0) return PLM_ERR_SHAPE;
     const size_t smem = (size_t)RL_TOKENS * K * sizeof(float);
     if (smem > 200 * 1024) return PLM_ERR_SHAPE;
-    const dim3 grid((n_tokens + RL_TOKENS - 1) / RL_TOKENS), nt(RL_WARPS * 32);
+    const dim3 grid((n_tokens + RL_TOKENS - 1) / RL_TOKENS, (E + RL_WARPS - 1) / RL_WARPS), nt(RL_WARPS * 32);
 #define RL_LAUNCH(Th_, Tw_)                                                                                            \
     do {                                                                                                               \
         if (smem > 48 * 1024)                                                                                          \

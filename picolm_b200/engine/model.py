@@ -71,12 +71,16 @@ class Model:
             part.load({rel: get(_join(prefix, rel)) for rel in part.weight_specs()})
         self.loaded = True
 
-    def weight_bytes_per_step(self) -> int:
+    def weight_bytes_per_step(self, tokens: int = 1) -> int:
         """Bytes of weights one decode step reads: every matrix of every scheduled
-        layer once, the norms, and the LM head (the embedding rows are negligible)."""
+        layer once, the norms, and the LM head (the embedding rows are negligible).  A part whose share grows with
+        the step's tokens (a routed feed-forward: every token may choose other experts) says so through
+        `weight_bytes_for(tokens)`, an upper bound."""
         total = self.final_norm.weight_bytes() + self.head.weight_bytes()
         for i in self.spec.schedule:
-            total += sum(part.weight_bytes() for _, part in self.blocks[i].parts())
+            for _, part in self.blocks[i].parts():
+                grows = getattr(part, "weight_bytes_for", None)
+                total += grows(tokens) if grows is not None else part.weight_bytes()
         return total
 
     # ------------------------------------------------------------------ cache

@@ -147,8 +147,13 @@ class RoutedMLP(Part):
 
     def weight_bytes(self):
         """What a decode step of one token reads: the router, `top` experts, the shared expert."""
+        return self.weight_bytes_for(1)
+
+    def weight_bytes_for(self, tokens: int) -> int:
+        """What a decode step of `tokens` tokens reads at most: each token's `top` experts, all different until all
+        experts are in use."""
         per = (self.w_gate_up.numel() + self.w_down.numel()) // self.E * self.w_down.element_size()
-        return (self.w_router.numel() * self.w_router.element_size() + self.top * per
+        return (self.w_router.numel() * self.w_router.element_size() + min(self.E, tokens * self.top) * per
                 + (self.shared.weight_bytes() if self.shared is not None else 0))
 
     def forward(self, h, step):
