@@ -52,8 +52,11 @@ class KunulornLayer:
 
     def to_dict(self) -> Dict[str, Any]:
         m = self.mixer
-        mixer = {"heads": m["heads"], "kv_heads": m["kv_heads"], "dim": m["dim"], "vdim": m["vdim"], "scale": m["scale"],
-                 "mask": {"size": m["mask_size"]}, "rot": {"base": m["rot_base"], "dims": m["rot_dims"]}}
+        mixer = {"heads": m["heads"], "kv_heads": m["kv_heads"], "dim": m["dim"], "vdim": m["vdim"], "scale": m["scale"]}
+        if m["mask_size"] is not None:
+            mixer["mask"] = {"size": m["mask_size"]}
+        if m["rot_dims"] or m.get("rot_given"):
+            mixer["rot"] = {"base": m["rot_base"], "dims": m["rot_dims"]}
         if m.get("kv_from") is not None:
             mixer["kv_from"] = m["kv_from"]
         return {"type": self.type, "mixer": mixer, "mlp": _plain(self.mlp)}
@@ -62,15 +65,21 @@ class KunulornLayer:
 def _read_mixer(m, where: str) -> Dict[str, Any]:
     out = {k: _positive(_need(m, k, where), f"{where}.{k}") for k in ("heads", "kv_heads", "dim", "vdim")}
     out["scale"] = float(_need(m, "scale", where))
-    out["mask_size"] = _positive(_need(_need(m, "mask", where), "size", where + ".mask"), f"{where}.mask.size")
-    rot = _need(m, "rot", where)
-    out["rot_base"] = _positive(_need(rot, "base", where + ".rot"), f"{where}.rot.base", float)
-    out["rot_dims"] = int(_need(rot, "dims", where + ".rot"))
+    # a mixer without `mask` sees every earlier key; one without `rot` rotates nothing
+    out["mask_size"] = None
+    if m.get("mask") is not None:
+        out["mask_size"] = _positive(_need(m["mask"], "size", where + ".mask"), f"{where}.mask.size")
+    out["rot_base"], out["rot_dims"] = 10000.0, 0
+    if m.get("rot") is not None:
+        rot = m["rot"]
+        out["rot_base"] = _positive(_need(rot, "base", where + ".rot"), f"{where}.rot.base", float)
+        out["rot_dims"] = int(_need(rot, "dims", where + ".rot"))
     if out["heads"] % out["kv_heads"]:
         raise ConfigError(f"config.json: {where}.heads is not a multiple of kv_heads")
     if out["rot_dims"] < 0 or out["rot_dims"] % 2 or out["rot_dims"] > out["dim"]:
         raise ConfigError(f"config.json: {where}.rot.dims must be even and at most dim")
     out["kv_from"] = None if m.get("kv_from") is None else int(m["kv_from"])
+    out["rot_given"] = m.get("rot") is not None
     return out
 
 
@@ -121,7 +130,7 @@ class KunulornConfig:
         eps = float(_need(_need(raw, "norm", "the model"), "eps", "norm"))
         if eps < 0:
             raise ConfigError("config.json: 'norm.eps' must not be negative")
-        scale = float(_need(_need(raw, "embedding", "the model"), "scale", "embedding"))
+        scale = float(_need(_need(raw, "embedding", "the model"), "scale", "embedding"))   # (named in full: a model says its scale)
         entries = _need(raw, "layers", "the model")
         if not isinstance(entries, (list, tuple)) or not entries:
             raise ConfigError("config.json: 'layers' must be a list with at least one layer")
