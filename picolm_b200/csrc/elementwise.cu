@@ -678,6 +678,9 @@ extern "C" int plm_add_bias(float* x, const float* bias, int n_rows, int d, cuda
 // written as zero (a zero component adds nothing to a score; a zero value column is multiplied by zero weights of
 // the output projection).  One block per token; the token's q and k sit in shared memory between the sums of
 // squares and the rotation; sums in an order that depends on the sizes only.
+__device__ __forceinline__ void store_pair(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
+__device__ __forceinline__ void store_pair(bf16* p, float a, float b) { *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b); }
+
 template <typename Ta, typename Tw, typename Tc, int NT>
 __global__ void __launch_bounds__(NT)
 qk_norm_rope_store_kernel(const Ta* __restrict__ qkv, const float* __restrict__ bias, const Tw* __restrict__ wq,
@@ -719,29 +722,18 @@ qk_norm_rope_store_kernel(const Ta* __restrict__ qkv, const float* __restrict__ 
     }
     const int rot_half = rot_dim / 2, half_c = hd_c / 2;
     const int heads = H + (own_kv ? G : 0);
-    // pairs of output components (ia, ib) of a head of hd_c: the rotated pairs first, then neighbours
-    for (int item = threadIdx.x; item < heads * half_c; item += NT) {
-        const int head = item / half_c, j = item - head * half_c;
-        int ia, ib;
-        const bool rotate = j < rot_half && cos_t != nullptr;
-        if (j < rot_half) {
-            if (pairing == 0) { ia = j; ib = j + rot_half; } else { ia = 2 * j; ib = 2 * j + 1; }
-        } else {
-            ia = rot_dim + 2 * (j - rot_half); ib = ia + 1;
-        }
+    // pairs of output components (ia, ib) of a head of hd_c: the rotated pairs first, then neighbours.  A warp takes a
+    // head, its lanes the head's pairs (no division a pair); neighbours are written as one 4- or 8-byte store.
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const float* cos_p = cos_t ? cos_t + (size_t)pos * rot_half : nullptr;
+    const float* sin_p = cos_t ? sin_t + (size_t)pos * rot_half : nullptr;
+    for (int head = warp; head < heads; head += NT / 32) {
         const bool is_q = head < H;
         const int hh = is_q ? head : head - H;
         const float* src = qk_sm + (is_q ? 0 : nq) + hh * D;
         const Tw* wn = is_q ? wq : wk;
+        if (wn) wn += hh * D;
         const float r = is_q ? rq : rk;
-        float a = 0.f, b = 0.f;
-        if (ia < D) { a = src[ia]; if (wn) a = a * r * to_f32<Tw>(wn[hh * D + ia]); }
-        if (ib < D) { b = src[ib]; if (wn) b = b * r * to_f32<Tw>(wn[hh * D + ib]); }
-        if (rotate) {
-            const float c = cos_t[(size_t)pos * rot_half + j], s = sin_t[(size_t)pos * rot_half + j];
-            const float ra = rope_first(a, b, c, s), rb = rope_second(a, b, c, s);
-            a = ra; b = rb;
-        }
         Tc* o;
         if (is_q) {
             o = q_out + ((size_t)t * H + hh) * hd_c;
@@ -749,8 +741,29 @@ qk_norm_rope_store_kernel(const Ta* __restrict__ qkv, const float* __restrict__ 
             if (!have_page) continue;
             o = kc + ((page_base + hh) * PLM_PAGE + in_page) * hd_c;
         }
-        o[ia] = from_f32<Tc>(a);
-        o[ib] = from_f32<Tc>(b);
+        for (int j = lane; j < half_c; j += 32) {
+            int ia, ib;
+            const bool rotate = j < rot_half && cos_p != nullptr;
+            if (j < rot_half) {
+                if (pairing == 0) { ia = j; ib = j + rot_half; } else { ia = 2 * j; ib = 2 * j + 1; }
+            } else {
+                ia = rot_dim + 2 * (j - rot_half); ib = ia + 1;
+            }
+            float a = 0.f, b = 0.f;
+            if (ia < D) { a = src[ia]; if (wn) a = a * r * to_f32<Tw>(wn[ia]); }
+            if (ib < D) { b = src[ib]; if (wn) b = b * r * to_f32<Tw>(wn[ib]); }
+            if (rotate) {
+                const float c = cos_p[j], s = sin_p[j];
+                const float ra = rope_first(a, b, c, s), rb = rope_second(a, b, c, s);
+                a = ra; b = rb;
+            }
+            if (ib == ia + 1) {
+                store_pair(o + ia, a, b);
+            } else {
+                o[ia] = from_f32<Tc>(a);
+                o[ib] = from_f32<Tc>(b);
+            }
+        }
     }
     if (own_kv && have_page) {
         for (int item = threadIdx.x; item < G * hd_c; item += NT) {

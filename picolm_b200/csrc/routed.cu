@@ -297,13 +297,24 @@ moe_gemm_kernel(const Ta* __restrict__ a, long lda, int top, const Tw* __restric
 }
 
 // ------------------------------------------------ the experts' products (mma.sync, few rows an expert)
-// The same two products for bfloat16 where an expert has few rows (decode steps): a tile of 16 sorted rows times 128
+// The same two products for bfloat16 where an expert has few rows (decode steps): a tile of 16 sorted rows times 64
 // columns of its expert's weights on `mma.sync.m16n8k16`, fp32 sums.  The weights are what the kernel moves (every
 // element is used once per tile), so they go from global memory straight into the B fragments, 16 bytes a thread and
 // row (eight consecutive k: two MMA steps, with the tile's rows read from shared memory in the same order of k);
 // the 16 rows sit in shared memory in pieces of 1,024 columns of K.  A row's sum has the same order wherever the row
 // lands.  N a multiple of 8, K a multiple of 32.
-constexpr int MM_WARPS = 8, MM_NB = 2, MM_BN = MM_WARPS * MM_NB * 8, MM_KC = 1024, MM_LD = MM_KC + 32;
+// (measured at 8 tokens x 3 of 32 experts of 2,048 x 2,048, gate/up and down together, cold L2: one block of eight columns a
+// warp and four steps of K unrolled 114 us; two blocks a warp 140 us; four 167 us; four warps a block 210 us; sixteen 118 us)
+#ifndef PLM_MM_NB
+#define PLM_MM_NB 1
+#endif
+#ifndef PLM_MM_WARPS
+#define PLM_MM_WARPS 8
+#endif
+#ifndef PLM_MM_UNROLL
+#define PLM_MM_UNROLL 4
+#endif
+constexpr int MM_WARPS = PLM_MM_WARPS, MM_NB = PLM_MM_NB, MM_BN = MM_WARPS * MM_NB * 8, MM_KC = 1024, MM_LD = MM_KC + 32;
 
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                                uint32_t b1) {
@@ -360,7 +371,9 @@ moe_gemm_mma_kernel(const bf16* __restrict__ a, long lda, int top, const bf16* _
         }
         __syncthreads();
         if (n_base < N) {
-#pragma unroll 2
+#define PLM_PRAGMA_(x) _Pragma(#x)
+#define PLM_UNROLL_(n) PLM_PRAGMA_(unroll n)
+            PLM_UNROLL_(PLM_MM_UNROLL)
             for (int k0 = 0; k0 < kn; k0 += 32) {
                 uint4 b[NACC][MM_NB];
 #pragma unroll
