@@ -106,7 +106,7 @@ class _Step:
 
 
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("d", [37, 192, 2304])
+@pytest.mark.parametrize("d", [37, 200, 2304])
 def test_layer_norm_kernel(out_dtype, d):
     """Mean, variance and weight; a delta and a projection's bias folded in and written back; gathered rows."""
     from picolm_b200 import ops
@@ -229,7 +229,7 @@ def test_clamped_gate_in_the_products_epilogue(T):
     ops.check_status()
 
 
-@pytest.mark.parametrize("E,top,groups,scale", [(16, 3, (4, 2), 1.5), (6, 2, (3, 2), 1.0), (8, 1, None, 2.5), (6, 2, (6, 3), 1.0),
+@pytest.mark.parametrize("E,top,groups,scale", [(16, 3, (4, 2), 1.75), (6, 2, (3, 2), 1.0), (8, 1, None, 2.5), (6, 2, (6, 3), 1.0),
                                                 (12, 4, (1, 1), 0.5), (64, 6, (8, 3), 2.0)])
 def test_router_choice_kernel(E, top, groups, scale):
     """Sigmoid scores, the correction for the choice only, groups by the sum of their two best, experts outside the
