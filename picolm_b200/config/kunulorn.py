@@ -140,8 +140,15 @@ class KunulornConfig:
             kind = _need(e, "type", where)
             if kind not in MIXER_TYPES:
                 raise ConfigError(f"config.json: {where}.type={kind!r} is not known ({', '.join(MIXER_TYPES)})")
-            layers.append(KunulornLayer(kind, _read_mixer(_need(e, "mixer", where), where + ".mixer"),
-                                        _read_mlp(e.get("mlp"), where + ".mlp")))
+            m = _need(e, "mixer", where)
+            j = m.get("kv_from") if isinstance(m, Mapping) else None
+            if isinstance(j, int) and 0 <= j < i and isinstance(entries[j].get("mixer"), Mapping):
+                # what a borrowing layer shares with the layer it borrows from may be left out of its entry
+                m = dict(m)
+                for key in ("kv_heads", "dim", "vdim", "rot"):
+                    if key not in m and key in entries[j]["mixer"]:
+                        m[key] = entries[j]["mixer"][key]
+            layers.append(KunulornLayer(kind, _read_mixer(m, where + ".mixer"), _read_mlp(e.get("mlp"), where + ".mlp")))
         for i, layer in enumerate(layers):
             j = layer.mixer["kv_from"]
             if j is None:

@@ -88,7 +88,8 @@ def attention_keys_values(h, W, m, eps):
     k = h @ W["k"].T + W["k.b"]
     v = h @ W["v"].T + W["v.b"]
     k = rms_norm(k, W["k.norm"], eps).reshape(T, G, D)
-    k = rotate_pairs(k, list(range(T)), m["rot"]["dims"], m["rot"]["base"])
+    if m.get("rot") is not None:                            # (a mixer whose configuration names no rotation has none)
+        k = rotate_pairs(k, list(range(T)), m["rot"]["dims"], m["rot"]["base"])
     return k, v.reshape(T, G, Dv)
 
 
@@ -98,9 +99,11 @@ def attention(h, W, m, eps, keys_values=None):
     H, G, D, Dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     q = h @ W["q"].T + W["q.b"]
     q = rms_norm(q, W["q.norm"], eps).reshape(T, H, D)
-    q = rotate_pairs(q, list(range(T)), m["rot"]["dims"], m["rot"]["base"])
+    if m.get("rot") is not None:
+        q = rotate_pairs(q, list(range(T)), m["rot"]["dims"], m["rot"]["base"])
     k, v = keys_values if keys_values is not None else attention_keys_values(h, W, m, eps)
-    mask = chunk_mask(T, m["mask"]["size"])
+    # (a mixer whose configuration names no mask sees every earlier key: one chunk as long as the sequence)
+    mask = chunk_mask(T, m["mask"]["size"] if m.get("mask") is not None else max(T, 1))
     out = torch.zeros(T, H, Dv, dtype=h.dtype)
     for head in range(H):
         g = head // (H // G)

@@ -426,6 +426,8 @@ MODELS = {
     # a width that no tensor map takes, an odd head size, no rotation in one layer, a rotation of the whole head in another
     "odd": ([_attn(heads=3, kv_heads=3, dim=10, vdim=6, rot=0, chunk=3), dict(_attn(heads=2, kv_heads=1, dim=12, vdim=20, rot=12, chunk=70), mlp=_moe(experts=5, top=2, groups=(1, 1), ff=9))],
             {"width": 42, "vocab": 101}),
+    # a mixer whose configuration names neither a mask nor a rotation: every earlier key, nothing turned
+    "plain_causal": ([{"type": "attention", "mixer": {"heads": 2, "kv_heads": 1, "dim": 16, "vdim": 16, "scale": 0.8}}, dict(_attn(chunk=40), mlp=_moe(groups=None))], {}),
     # head sizes that take the tensor-core kernels in bfloat16 runs (their float32 twins run here)
     "wide_heads": ([_attn(heads=2, kv_heads=1, dim=64, vdim=64, rot=32, chunk=50, scale=0.3), _attn(heads=2, kv_heads=2, dim=32, vdim=128, rot=32, chunk=130, scale=0.4)],
                    {"width": 64}),
