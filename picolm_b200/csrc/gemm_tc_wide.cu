@@ -307,6 +307,13 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     __shared__ int s_abort, s_parts_missing;
 
     pdl_launch_dependents();
+    // Which tile of tokens and which of features a tile number is.  Plain form: the token tiles of one range of features
+    // follow each other, so that CTAs that run at the same time share its weights.  Grouped form: the feature tiles of one
+    // tile of tokens follow each other; the token tiles of one group are neighbours, so one wave of CTAs holds all tiles that
+    // read a group's weights, each weight comes from memory once, and the token rows stay in the L2 (measured at 6,144 rows
+    // over 32 groups of 4,096 x 2,048: the other order read 800 MB where the weights are 537 MB).
+    auto tile_m = [&](int tile) { return tile_group ? tile / n_tiles : tile % m_tiles; };
+    auto tile_n = [&](int tile) { return tile_group ? tile % n_tiles : tile / m_tiles; };
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_kb = (K + BK * SLABS - 1) / (BK * SLABS);                // stages of K
     const uint32_t rank = PAIR ? cluster_rank() : 0u;                    // rank 0 of a pair issues the MMAs
@@ -363,11 +370,11 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             Walk walk = walk0;
             Piece w;
             while (ok && walk.next(w)) {
-                const int m0 = (w.tile % m_tiles) * TILE_M + (int)rank * BM;
-                int f0 = (w.tile / m_tiles) * BN + (int)rank * W_ROWS;
+                const int m0 = tile_m(w.tile) * TILE_M + (int)rank * BM;
+                int f0 = tile_n(w.tile) * BN + (int)rank * W_ROWS;
                 if (tile_group) {
                     if (!waited) { pdl_wait(); waited = true; }
-                    const int grp = tile_group[w.tile % m_tiles];
+                    const int grp = tile_group[tile_m(w.tile)];
                     if (grp < 0) continue;                               // a tile without rows: every role passes it by
                     f0 += grp * group_rows;
                 }
@@ -439,7 +446,7 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 #endif
             if (tile_group) pdl_wait();                                  // an earlier kernel of the step writes it
             for (; ok && walk.next(w); ++j) {
-                if (tile_group && tile_group[w.tile % m_tiles] < 0) { --j; continue; }
+                if (tile_group && tile_group[tile_m(w.tile)] < 0) { --j; continue; }
                 const int acc = j & 1;
                 // the epilogue must have read this accumulator's previous piece out
                 if (!mbar_wait(acc_empty0 + 8 * acc, ((j >> 1) & 1) ^ 1, status, 2)) { s_abort = 1; ok = false; break; }
@@ -489,9 +496,9 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         Walk walk = walk0;
         Piece w;
         for (; ok && walk.next(w); ++j) {
-            if (tile_group && tile_group[w.tile % m_tiles] < 0) { --j; continue; }
+            if (tile_group && tile_group[tile_m(w.tile)] < 0) { --j; continue; }
             const int acc = j & 1;
-            const int m0 = (w.tile % m_tiles) * TILE_M + (int)rank * BM, f0 = (w.tile / m_tiles) * BN;
+            const int m0 = tile_m(w.tile) * TILE_M + (int)rank * BM, f0 = tile_n(w.tile) * BN;
             const int row0 = m0 + quarter * 32;                          // this warp's 32 token rows
             const uint32_t tacc = tmem_base + lane_bits + acc * BN;
             // an owner's tile: the parts that the CTAs after this one left, once their flags are up (they are
