@@ -119,6 +119,12 @@ route_topk_kernel(const float* __restrict__ logits, int ld, const float* __restr
 // tokens a block with their rows of h in shared memory as fp32, a warp per row of w (blockIdx.y: which eight rows), lanes
 // over k and a shuffle tree at the end, so that a logit's sum has the same order in every batch.
 constexpr int RL_TOKENS = 4, RL_WARPS = 8;
+__device__ __forceinline__ float4 rl_load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 rl_load4(const bf16* p) {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&u.x), b = *reinterpret_cast<const __nv_bfloat162*>(&u.y);
+    return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+}
 template <typename Th, typename Tw>
 __global__ void __launch_bounds__(RL_WARPS * 32)
 router_logits_kernel(const Th* __restrict__ h, const Tw* __restrict__ w, float* __restrict__ out, int T, int E, int K) {
@@ -126,9 +132,10 @@ router_logits_kernel(const Th* __restrict__ h, const Tw* __restrict__ w, float* 
     pdl_launch_dependents();
     pdl_wait();
     const int t0 = blockIdx.x * RL_TOKENS, nt = min(RL_TOKENS, T - t0);
-    for (int i = threadIdx.x; i < RL_TOKENS * K; i += RL_WARPS * 32) {
-        const int tt = i / K, k = i - tt * K;
-        rl_sm[i] = tt < nt ? to_f32<Th>(h[(size_t)(t0 + tt) * K + k]) : 0.f;
+#pragma unroll
+    for (int tt = 0; tt < RL_TOKENS; ++tt) {
+        const Th* hr = h + (size_t)(t0 + (tt < nt ? tt : 0)) * K;
+        for (int k = threadIdx.x; k < K; k += RL_WARPS * 32) rl_sm[tt * K + k] = tt < nt ? to_f32<Th>(hr[k]) : 0.f;
     }
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -137,11 +144,27 @@ router_logits_kernel(const Th* __restrict__ h, const Tw* __restrict__ w, float* 
         float acc[RL_TOKENS];
 #pragma unroll
         for (int tt = 0; tt < RL_TOKENS; ++tt) acc[tt] = 0.f;
-#pragma unroll 4
-        for (int k = lane; k < K; k += 32) {
-            const float wv = to_f32<Tw>(wr[k]);
+        if (K % 4 == 0 && ((uintptr_t)w & 15) == 0) {
+            // four consecutive k a lane and step: one 8- or 16-byte load of the weights, one 16-byte load a token
+#pragma unroll 2
+            for (int k = lane * 4; k < K; k += 128) {
+                const float4 wv = rl_load4(wr + k);
 #pragma unroll
-            for (int tt = 0; tt < RL_TOKENS; ++tt) acc[tt] = fmaf(rl_sm[tt * K + k], wv, acc[tt]);
+                for (int tt = 0; tt < RL_TOKENS; ++tt) {
+                    const float4 hv = *reinterpret_cast<const float4*>(rl_sm + tt * K + k);
+                    acc[tt] = fmaf(hv.x, wv.x, acc[tt]);
+                    acc[tt] = fmaf(hv.y, wv.y, acc[tt]);
+                    acc[tt] = fmaf(hv.z, wv.z, acc[tt]);
+                    acc[tt] = fmaf(hv.w, wv.w, acc[tt]);
+                }
+            }
+        } else {
+#pragma unroll 4
+            for (int k = lane; k < K; k += 32) {
+                const float wv = to_f32<Tw>(wr[k]);
+#pragma unroll
+                for (int tt = 0; tt < RL_TOKENS; ++tt) acc[tt] = fmaf(rl_sm[tt * K + k], wv, acc[tt]);
+            }
         }
 #pragma unroll
         for (int tt = 0; tt < RL_TOKENS; ++tt) {
@@ -444,6 +467,24 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, long ldy, const 
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
+    if (d % 4 == 0 && ldy % 4 == 0 && ((((uintptr_t)y | (uintptr_t)shared | (uintptr_t)out) & 15) == 0)) {
+        // four columns a thread (the same sums in the same order)
+        for (int i = threadIdx.x * 4; i < d; i += blockDim.x * 4) {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int k = 0; k < top; ++k) {
+                const float wk = weights[(size_t)t * top + k];
+                const float4 v = *reinterpret_cast<const float4*>(y + (size_t)where[(size_t)t * top + k] * ldy + i);
+                acc.x = fmaf(wk, v.x, acc.x); acc.y = fmaf(wk, v.y, acc.y); acc.z = fmaf(wk, v.z, acc.z); acc.w = fmaf(wk, v.w, acc.w);
+            }
+            if (shared) {
+                const float gt = gate ? gate[t] : 1.0f;
+                const float4 v = *reinterpret_cast<const float4*>(shared + (size_t)t * d + i);
+                acc.x = fmaf(gt, v.x, acc.x); acc.y = fmaf(gt, v.y, acc.y); acc.z = fmaf(gt, v.z, acc.z); acc.w = fmaf(gt, v.w, acc.w);
+            }
+            *reinterpret_cast<float4*>(out + (size_t)t * d + i) = acc;
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < d; i += blockDim.x) {
         float acc = 0.f;
         for (int k = 0; k < top; ++k)
