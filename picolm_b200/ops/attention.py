@@ -14,7 +14,8 @@ from ._lib import (PAGE_TOKENS, SM_COUNT, KernelError, _check, _dev, _dt, _fn, _
 def attention_rows(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, tok_pos: torch.Tensor,
                    tok_seq: torch.Tensor, block_table: torch.Tensor, num_kv_heads: int, scale: float,
                    window: Optional[int] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Causal attention of q [T, H, hd] over the paged cache; returns [T, H*hd]."""
+    """Causal attention of q [T, H, hd] over the paged cache; returns [T, H*hd].  `window` here and in the other kernels' faces:
+    a sliding window of that many keys, or the negative of a chunk size for a mask of chunks (`key_mask`)."""
     _dev(q, "q"), _dev(k_cache, "k_cache"), _dev(v_cache, "v_cache")
     _i32(tok_pos, "tok_pos"), _i32(tok_seq, "tok_seq"), _i32(block_table, "block_table")
     T, H, hd = q.shape
